@@ -1,0 +1,113 @@
+/*
+ * C ABI of the B200 (sm_100a) document-masked flash-attention library.
+ *
+ * The library replaces the four Triton launches of the reference operator
+ * (flash_triton.py:541 `_fwd_kernel`, :585 `_bwd_preprocess`, :596 `_bwd_kv_kernel`,
+ * :617 `_bwd_q_kernel`) and adds the mask plan (per-block id ranges, no counterpart in the
+ * reference: README.md:18 lists block sparsity as not implemented).
+ *
+ * Conventions
+ *  - every pointer is a device pointer of the current CUDA device unless stated otherwise;
+ *  - tensors are [B, H, L, D] with ELEMENT strides; the last stride must be 1, the other
+ *    strides multiples of 8 elements and the base 16-byte aligned (TMA rules);
+ *  - the caller owns every buffer;
+ *  - every function enqueues on `stream` and returns without synchronising;
+ *  - return value 0 = ok, otherwise an FA_ERR_* code (fa_error_string() describes it);
+ *  - `status` is one int32 in device memory, zeroed by the caller. Kernels write a non-zero
+ *    code there when a bounded wait ran out (100..199) or an id was out of range (200).
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_VERSION 1
+
+enum fa_dtype { FA_BF16 = 0, FA_FP16 = 1 };
+enum fa_id_dtype { FA_ID_NONE = 0, FA_ID_INT32 = 1, FA_ID_INT64 = 2 };
+/* score_func_mode of the reference (flash_triton.py:20-22) */
+enum fa_mode { FA_MODE0_NOPE = 0, FA_MODE1_DOC = 1 };
+
+enum fa_error {
+    FA_OK = 0,
+    FA_ERR_BAD_ARG = 1,      /* null pointer, non-positive size, unknown enum */
+    FA_ERR_UNSUPPORTED = 2,  /* head dim not in {64,128}, dtype not bf16/fp16, sm_scale <= 0 */
+    FA_ERR_ALIGNMENT = 3,    /* a base address or stride breaks the TMA 16-byte rules */
+    FA_ERR_TENSORMAP = 4,    /* the driver refused to encode a tensor map */
+    FA_ERR_LAUNCH = 5,       /* kernel launch failed (cudaGetLastError) */
+    FA_ERR_PLAN_SIZE = 6,    /* plan buffer too small / missing for FA_MODE1_DOC */
+    FA_ERR_NO_DRIVER = 7     /* cuTensorMapEncodeTiled could not be resolved */
+};
+
+typedef struct fa_problem {
+    int32_t B, H, Hk; /* batch, query heads, key/value heads (H % Hk == 0) */
+    int32_t M, N, D;  /* query length, key length, head dim */
+    int32_t dtype;    /* enum fa_dtype, of q/k/v/o and all gradients */
+    int32_t causal;   /* bottom-right aligned: query i sees key j iff j <= i + max(0, N-M) */
+    int32_t mode;     /* enum fa_mode */
+    int32_t id_heads; /* head extent of the id tensors as stored in the plan: 1 (broadcast) or H */
+    float sm_scale;   /* > 0 */
+} fa_problem;
+
+typedef struct fa_tensor {
+    void* ptr;
+    int64_t stride[4]; /* elements, order [B, H, L, D] */
+} fa_tensor;
+
+typedef struct fa_ids {
+    const void* ptr;
+    int64_t stride[3]; /* elements, order [B, H, L]; any value incl. 0 */
+    int32_t dtype;     /* enum fa_id_dtype */
+} fa_ids;
+
+int fa_version(void);
+const char* fa_error_string(int code);
+
+/* Rows of the internal per-row fp32 buffers (log-sum-exp, delta): M rounded up to 128. */
+int64_t fa_padded_rows(int32_t M);
+
+/* Size in bytes of the mask plan for this problem (0 when mode == FA_MODE0_NOPE). */
+int fa_plan_bytes(const fa_problem* p, size_t* bytes);
+
+/* Builds the mask plan from eq [B,H,M] / ek [B,H,N]: 32-bit id codes, per-128-block id
+ * min/max, and per-block ranges of blocks that hold at least one unmasked entry.
+ * Mask rule (flash_triton.py:114, README.md:16): keep = (eq >= 0) | (eq == ek). */
+int fa_plan_build(const fa_problem* p, const fa_ids* eq, const fa_ids* ek, void* plan, size_t plan_bytes,
+                  int32_t* status, void* stream);
+
+/* Forward (replaces flash_triton.py:541). o has q's shape; lse is [B, H, fa_padded_rows(M)] fp32,
+ * log2-domain log-sum-exp of the scaled scores (flash_triton.py:133), -inf for a row with no
+ * unmasked key (whose output row is 0). plan may be NULL when mode == FA_MODE0_NOPE. */
+int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
+           const fa_tensor* o, float* lse, const void* plan, int32_t* status, void* stream);
+
+/* delta[b,h,i] = sum_d o*do in fp32 (replaces flash_triton.py:585); delta is
+ * [B, H, fa_padded_rows(M)], padding rows are written as 0. */
+int fa_bwd_delta(const fa_problem* p, const fa_tensor* o, const fa_tensor* d_o, float* delta, void* stream);
+
+/* dK, dV [B, Hk, N, D] (replaces flash_triton.py:596 and the group sum at :635-637; the sum
+ * over the query heads of a group is accumulated in fp32 inside the kernel). */
+int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
+                const fa_tensor* d_o, const float* lse, const float* delta, const fa_tensor* dk,
+                const fa_tensor* dv, const void* plan, int32_t* status, void* stream);
+
+/* dQ [B, H, M, D] (replaces flash_triton.py:617). */
+int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
+              const fa_tensor* d_o, const float* lse, const float* delta, const fa_tensor* dq,
+              const void* plan, int32_t* status, void* stream);
+
+/* Debug: materialise the kernels' decisions. keep is [B, id_heads, M, N] bytes (1 = unmasked),
+ * produced by the same device predicate the attention kernels use; tile_class is
+ * [B, id_heads, ceil(M/128), ceil(N/128)] bytes: bit0 visited, bit1 bound/causal check,
+ * bit2 id check, bit3 query tail. Either pointer may be NULL. */
+int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */

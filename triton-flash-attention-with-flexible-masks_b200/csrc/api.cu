@@ -1,0 +1,279 @@
+// extern "C" surface of the library (declared in include/fa_b200.h): argument checks, TMA
+// tensor-map encoding, parameter packing and launches. Nothing here allocates or synchronises.
+#include <mutex>
+#include "../../include/fa_b200.h"
+#include "common.cuh"
+#include "params.cuh"
+
+namespace fa {
+cudaError_t launch_plan_build(const void*, const int64_t*, int, const void*, const int64_t*, int, int32_t*,
+                              const PlanLayout&, int, int, int*, cudaStream_t);
+cudaError_t launch_debug_mask(const MaskArgs&, uint8_t*, uint8_t*, cudaStream_t);
+cudaError_t launch_fwd(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FwdParams&,
+                       int, cudaStream_t);
+cudaError_t launch_bwd_delta(const DeltaParams&, cudaStream_t);
+cudaError_t launch_bwd_dkdv(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                            const CUtensorMap&, const DkdvParams&, int, cudaStream_t);
+cudaError_t launch_bwd_dq(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                          const CUtensorMap&, const DqParams&, int, cudaStream_t);
+}  // namespace fa
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is resolved through the runtime so that the library has no link-time
+// dependency on libcuda (it must load, and list its symbols, on a machine without a driver).
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    });
+    return fn;
+}
+
+int check_problem(const fa_problem* p) {
+    if (!p) return FA_ERR_BAD_ARG;
+    if (p->B <= 0 || p->H <= 0 || p->Hk <= 0 || p->M <= 0 || p->N <= 0) return FA_ERR_BAD_ARG;
+    if (p->H % p->Hk != 0) return FA_ERR_BAD_ARG;
+    if (p->mode != FA_MODE0_NOPE && p->mode != FA_MODE1_DOC) return FA_ERR_BAD_ARG;
+    if (p->id_heads != 1 && p->id_heads != p->H) return FA_ERR_BAD_ARG;
+    if (p->causal && p->N < p->M) return FA_ERR_BAD_ARG;  // flash_triton.py:520
+    if (p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
+    if (p->dtype != FA_BF16 && p->dtype != FA_FP16) return FA_ERR_UNSUPPORTED;
+    if (!(p->sm_scale > 0.f)) return FA_ERR_UNSUPPORTED;
+    if (fa::cdiv(p->N, fa::kBlk) > fa::kListCap || fa::cdiv(p->M, fa::kBlk) > fa::kListCap)
+        return FA_ERR_UNSUPPORTED;  // at most 1024 blocks (131072 tokens) per sequence
+    if (p->H > 65535 || p->B > 65535) return FA_ERR_UNSUPPORTED;
+    return FA_OK;
+}
+
+int check_tensor(const fa_tensor* t, int B, int H, int L) {
+    if (!t || !t->ptr) return FA_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(t->ptr) % 16 != 0) return FA_ERR_ALIGNMENT;
+    if (t->stride[3] != 1) return FA_ERR_ALIGNMENT;
+    const int ext[3] = {B, H, L};
+    for (int i = 0; i < 3; ++i) {
+        if (ext[i] > 1 && (t->stride[i] <= 0 || t->stride[i] % 8 != 0)) return FA_ERR_ALIGNMENT;
+    }
+    return FA_OK;
+}
+
+// 4-D map over [B, H, L, D]; box = 64 elements of D x 128 rows of L; 128-byte swizzle; rows
+// outside [0, L) read as zero.
+int make_map(CUtensorMap* out, const fa_tensor* t, int dtype, int B, int H, int L, int D) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return FA_ERR_NO_DRIVER;
+    const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(L), cuuint64_t(H), cuuint64_t(B)};
+    // extent-1 dimensions may carry any stride in the caller's view; give the driver a sane one
+    const int64_t sl = (L > 1) ? t->stride[2] : D;
+    const int64_t sh = (H > 1) ? t->stride[1] : sl * L;
+    const int64_t sb = (B > 1) ? t->stride[0] : sh * H;
+    const cuuint64_t strides[3] = {cuuint64_t(sl) * 2, cuuint64_t(sh) * 2, cuuint64_t(sb) * 2};
+    const cuuint32_t box[4] = {64, cuuint32_t(fa::kBlk), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r =
+        fn(out, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, t->ptr,
+           dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FA_OK : FA_ERR_TENSORMAP;
+}
+
+int make_mask(fa::MaskArgs* m, const fa_problem* p, const void* plan) {
+    if (p->mode == FA_MODE1_DOC && !plan) return FA_ERR_PLAN_SIZE;
+    m->plan = (p->mode == FA_MODE1_DOC) ? static_cast<const int32_t*>(plan) : nullptr;
+    m->He = (p->mode == FA_MODE1_DOC) ? p->id_heads : 1;
+    m->L = fa::PlanLayout(p->B, m->He, p->M, p->N);
+    m->M = p->M;
+    m->N = p->N;
+    m->gap = p->N > p->M ? p->N - p->M : 0;  // flash_triton.py:521
+    m->causal = p->causal ? 1 : 0;
+    m->mode = p->mode;
+    return FA_OK;
+}
+
+fa::OutTensor out_view(const fa_tensor* t) { return fa::OutTensor{t->ptr, t->stride[0], t->stride[1], t->stride[2]}; }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+}  // namespace
+
+extern "C" {
+
+int fa_version(void) { return FA_VERSION; }
+
+const char* fa_error_string(int code) {
+    switch (code) {
+        case FA_OK: return "ok";
+        case FA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, H % Hk != 0, causal with N < M)";
+        case FA_ERR_UNSUPPORTED:
+            return "unsupported problem (head dim must be 64 or 128, dtype bf16/fp16, sm_scale > 0, "
+                   "at most 131072 tokens per sequence)";
+        case FA_ERR_ALIGNMENT:
+            return "tensor breaks the TMA rules (16-byte aligned base, last stride 1, other strides multiples of 8)";
+        case FA_ERR_TENSORMAP: return "cuTensorMapEncodeTiled failed";
+        case FA_ERR_LAUNCH: return "kernel launch failed";
+        case FA_ERR_PLAN_SIZE: return "mask plan missing or too small";
+        case FA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled not available";
+        default: return "unknown error";
+    }
+}
+
+int64_t fa_padded_rows(int32_t M) { return fa::pad128(M); }
+
+int fa_plan_bytes(const fa_problem* p, size_t* bytes) {
+    if (!bytes) return FA_ERR_BAD_ARG;
+    const int rc = check_problem(p);
+    if (rc) return rc;
+    if (p->mode == FA_MODE0_NOPE) {
+        *bytes = 0;
+        return FA_OK;
+    }
+    fa::PlanLayout L(p->B, p->id_heads, p->M, p->N);
+    *bytes = size_t(L.total) * sizeof(int32_t);
+    return FA_OK;
+}
+
+int fa_plan_build(const fa_problem* p, const fa_ids* eq, const fa_ids* ek, void* plan, size_t plan_bytes,
+                  int32_t* status, void* stream) {
+    const int rc = check_problem(p);
+    if (rc) return rc;
+    if (p->mode != FA_MODE1_DOC) return FA_OK;
+    if (!eq || !ek || !eq->ptr || !ek->ptr || !plan || !status) return FA_ERR_BAD_ARG;
+    if ((eq->dtype != FA_ID_INT32 && eq->dtype != FA_ID_INT64) || (ek->dtype != FA_ID_INT32 && ek->dtype != FA_ID_INT64))
+        return FA_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(plan) % 16 != 0) return FA_ERR_ALIGNMENT;
+    fa::PlanLayout L(p->B, p->id_heads, p->M, p->N);
+    if (plan_bytes < size_t(L.total) * sizeof(int32_t)) return FA_ERR_PLAN_SIZE;
+    const int gap = p->N > p->M ? p->N - p->M : 0;
+    const cudaError_t e = fa::launch_plan_build(eq->ptr, eq->stride, eq->dtype == FA_ID_INT64, ek->ptr, ek->stride,
+                                                ek->dtype == FA_ID_INT64, static_cast<int32_t*>(plan), L, gap,
+                                                p->causal ? 1 : 0, status, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v, const fa_tensor* o,
+           float* lse, const void* plan, int32_t* status, void* stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!lse || !status) return FA_ERR_BAD_ARG;
+    if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(v, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(o, p->B, p->H, p->M))) return rc;
+    fa::FwdParams fp;
+    if ((rc = make_mask(&fp.mask, p, plan))) return rc;
+    CUtensorMap tq, tk, tv;
+    if ((rc = make_map(&tq, q, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    fp.o = out_view(o);
+    fp.lse = lse;
+    fp.H = p->H;
+    fp.G = p->H / p->Hk;
+    fp.scale_log2 = p->sm_scale * kLog2e;
+    fp.status = status;
+    const cudaError_t e =
+        fa::launch_fwd(p->D, p->dtype == FA_BF16, tq, tk, tv, fp, p->B, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+int fa_bwd_delta(const fa_problem* p, const fa_tensor* o, const fa_tensor* d_o, float* delta, void* stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!delta) return FA_ERR_BAD_ARG;
+    if ((rc = check_tensor(o, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
+    fa::DeltaParams dp;
+    dp.o = out_view(o);
+    dp.d_o = out_view(d_o);
+    dp.delta = delta;
+    dp.B = p->B; dp.H = p->H; dp.M = p->M; dp.D = p->D;
+    dp.Mpad = fa::pad128(p->M);
+    dp.bf16 = p->dtype == FA_BF16;
+    const cudaError_t e = fa::launch_bwd_delta(dp, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
+                const fa_tensor* d_o, const float* lse, const float* delta, const fa_tensor* dk, const fa_tensor* dv,
+                const void* plan, int32_t* status, void* stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
+    if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(v, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(dk, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(dv, p->B, p->Hk, p->N))) return rc;
+    fa::DkdvParams kp;
+    if ((rc = make_mask(&kp.mask, p, plan))) return rc;
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, q, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    if ((rc = make_map(&tdo, d_o, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    kp.dk = out_view(dk);
+    kp.dv = out_view(dv);
+    kp.lse = lse;
+    kp.delta = delta;
+    kp.H = p->H;
+    kp.Hk = p->Hk;
+    kp.G = p->H / p->Hk;
+    kp.scale_log2 = p->sm_scale * kLog2e;
+    kp.sm_scale = p->sm_scale;
+    kp.status = status;
+    const cudaError_t e =
+        fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, kp, p->B, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v, const fa_tensor* d_o,
+              const float* lse, const float* delta, const fa_tensor* dq, const void* plan, int32_t* status,
+              void* stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
+    if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(dq, p->B, p->H, p->M))) return rc;
+    if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
+    if ((rc = check_tensor(v, p->B, p->Hk, p->N))) return rc;
+    fa::DqParams qp;
+    if ((rc = make_mask(&qp.mask, p, plan))) return rc;
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, q, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    if ((rc = make_map(&tdo, d_o, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    qp.dq = out_view(dq);
+    qp.lse = lse;
+    qp.delta = delta;
+    qp.H = p->H;
+    qp.G = p->H / p->Hk;
+    qp.scale_log2 = p->sm_scale * kLog2e;
+    qp.sm_scale = p->sm_scale;
+    qp.status = status;
+    const cudaError_t e =
+        fa::launch_bwd_dq(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, qp, p->B, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    fa::MaskArgs m;
+    if ((rc = make_mask(&m, p, plan))) return rc;
+    const cudaError_t e = fa::launch_debug_mask(m, keep, tile_class, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
+}  // extern "C"

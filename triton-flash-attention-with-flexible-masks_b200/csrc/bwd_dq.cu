@@ -1,0 +1,331 @@
+// dQ kernel. Replaces `_bwd_q_kernel` (flash_triton.py:323-431): per block of 128 queries,
+// walk the visited key tiles, recompute P = exp2(S*scale*log2e - LSE), dP = dO V^T,
+// dS = P * (dP - delta) with masked entries zeroed, dQ += dS K, and scale by sm_scale at the end.
+//
+// One CTA = one query block of one (batch, head), 12 warps:
+//   warps 0-7  two compute groups; thread r of group g owns query row r and key columns
+//              [64g, 64g+64) of every tile
+//   warp 8     TMA producer (Q and dO once, K ring, V ring)
+//   warp 9     tcgen05.mma issuer, owns TMEM
+// TMEM columns: S0 [0,128) S1 [128,256) dP [256,384) dQ [384,384+D). dS (input dtype) is
+// written over the first half of each group's own S columns and fed to the dQ MMA from TMEM.
+#include "common.cuh"
+#include "params.cuh"
+
+namespace fa {
+
+template <int D>
+struct DqSmem {
+    static constexpr int NSK = (D == 128) ? 3 : 4;
+    static constexpr int NSV = (D == 128) ? 2 : 4;
+    static constexpr int TILE = kBlk * D * 2;
+    static constexpr int BOX = kBlk * 64 * 2;
+    static constexpr int NBOX = D / 64;
+    static constexpr int off_q = 0;
+    static constexpr int off_do = TILE;
+    static constexpr int off_k = 2 * TILE;
+    static constexpr int off_v = off_k + NSK * TILE;
+    static constexpr int off_list = off_v + NSV * TILE;
+    static constexpr int off_bar = off_list + kListCap * 2;
+    // qdo_full, k_full[NSK], v_full[NSV], k_empty[NSK], v_empty[NSV], s_full[2], ds_full[2], dp_full, done
+    static constexpr int n_bar = 1 + 2 * NSK + 2 * NSV + 6;
+    static constexpr int off_misc = off_bar + n_bar * 8;
+    static constexpr int total = off_misc + 16;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const DqParams p) {
+    using S = DqSmem<D>;
+    constexpr int NSK = S::NSK, NSV = S::NSV;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const MaskArgs& mk = p.mask;
+    const int qb = mk.L.nQ - 1 - int(blockIdx.x);
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / p.G;
+    const int he = (mk.He == 1) ? 0 : h;
+
+    uint16_t* list = reinterpret_cast<uint16_t*>(smem + S::off_list);
+    volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);
+    const uint32_t bar0 = sbase + S::off_bar;
+    auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
+    const int B_QDO = 0, B_KFULL = 1, B_VFULL = B_KFULL + NSK, B_KEMPTY = B_VFULL + NSV, B_VEMPTY = B_KEMPTY + NSK,
+              B_SFULL = B_VEMPTY + NSV, B_DSFULL = B_SFULL + 2, B_DPFULL = B_DSFULL + 2, B_DONE = B_DPFULL + 1;
+    Abort ab{misc + 1, p.status};
+
+    int lo, hi;
+    kv_range(mk, b, he, qb, lo, hi);
+    int n = hi - lo;
+    if (n > kListCap) n = kListCap;
+
+    if (tid == 0) {
+        mbar_init(BAR(B_QDO), 1);
+        for (int s = 0; s < NSK; ++s) { mbar_init(BAR(B_KFULL + s), 1); mbar_init(BAR(B_KEMPTY + s), 1); }
+        for (int s = 0; s < NSV; ++s) { mbar_init(BAR(B_VFULL + s), 1); mbar_init(BAR(B_VEMPTY + s), 1); }
+        for (int w = 0; w < 2; ++w) { mbar_init(BAR(B_SFULL + w), 1); mbar_init(BAR(B_DSFULL + w), 256); }
+        mbar_init(BAR(B_DPFULL), 1);
+        mbar_init(BAR(B_DONE), 1);
+        misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
+        misc[2] = 0;
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(sbase + S::off_misc, 512);
+        tmem_relinquish();
+    }
+    for (int i = tid; i < n; i += kAttnThreads) list[i] = uint16_t(classify_from_plan(mk, b, he, qb, lo + i));
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) {
+        const int Tn = compact_visit_list(list, n, lane);
+        if (lane == 0) misc[2] = Tn;
+    }
+    __syncthreads();
+    const uint32_t tmem = uint32_t(misc[0]);
+    const int T = misc[2];
+    const bool aborted = misc[1] != 0;
+
+    const uint32_t sQ = sbase + S::off_q, sdO = sbase + S::off_do;
+    auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };
+    auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
+
+    if (warp >= 8) {
+        setmaxnreg_dec<56>();
+        if (aborted || T == 0) {
+        } else if (warp == 8) {
+            // ------------------------------ TMA producer ------------------------------
+            if (lane == 0) {
+                tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+                mbar_expect_tx(BAR(B_QDO), 2 * S::TILE);
+                for (int x = 0; x < S::NBOX; ++x) {
+                    tma_load_4d(sQ + x * S::BOX, &tmQ, BAR(B_QDO), x * 64, qb * kBlk, h, b);
+                    tma_load_4d(sdO + x * S::BOX, &tmdO, BAR(B_QDO), x * 64, qb * kBlk, h, b);
+                }
+                bool ok = true;
+                for (int t = 0; t <= T && ok; ++t) {  // K runs one tile ahead of V
+                    if (t < T) {
+                        const int kb = lo + (list[t] & 1023);
+                        const int st = t % NSK, use = t / NSK;
+                        if (use > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 21);
+                        if (!ok) break;
+                        mbar_expect_tx(BAR(B_KFULL + st), S::TILE);
+                        for (int x = 0; x < S::NBOX; ++x)
+                            tma_load_4d(sK(st) + x * S::BOX, &tmK, BAR(B_KFULL + st), x * 64, kb * kBlk, hk, b);
+                    }
+                    if (t >= 1) {
+                        const int tv = t - 1;
+                        const int kb = lo + (list[tv] & 1023);
+                        const int st = tv % NSV, use = tv / NSV;
+                        if (use > 0) ok = mbar_wait(BAR(B_VEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 22);
+                        if (!ok) break;
+                        mbar_expect_tx(BAR(B_VFULL + st), S::TILE);
+                        for (int x = 0; x < S::NBOX; ++x)
+                            tma_load_4d(sV(st) + x * S::BOX, &tmV, BAR(B_VFULL + st), x * 64, kb * kBlk, hk, b);
+                    }
+                }
+            }
+        } else if (warp == 9) {
+            // ------------------------------ MMA issuer ------------------------------
+            if (lane == 0) {
+                constexpr uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
+                constexpr uint32_t idesc_dq = make_idesc(BF16, 128, D, false, true);
+                constexpr uint64_t desc_mn = desc_mn_major(S::BOX);
+                bool ok = mbar_wait(BAR(B_QDO), 0, ab, ST_WAIT_TIMEOUT + 23);
+                auto issue_s = [&](int t) {
+                    const int st = t % NSK, use = t / NSK;
+                    if (!mbar_wait(BAR(B_KFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 24)) return false;
+                    tc_fence_after();
+                    const uint32_t d = tmem + uint32_t(t & 1) * 128u;
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
+                        umma_ss(d, smem_desc_at(kDescKMajor, sQ + off), smem_desc_at(kDescKMajor, sK(st) + off),
+                                idesc_s, kk > 0);
+                    }
+                    umma_commit(BAR(B_SFULL + (t & 1)));
+                    return true;
+                };
+                auto issue_dp = [&](int t) {
+                    const int st = t % NSV, use = t / NSV;
+                    if (!mbar_wait(BAR(B_VFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 25)) return false;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
+                        umma_ss(tmem + 256u, smem_desc_at(kDescKMajor, sdO + off),
+                                smem_desc_at(kDescKMajor, sV(st) + off), idesc_s, kk > 0);
+                    }
+                    umma_commit(BAR(B_VEMPTY + st));
+                    umma_commit(BAR(B_DPFULL));
+                    return true;
+                };
+                auto issue_dq = [&](int t) {
+                    const int st = t % NSK;
+                    const uint32_t a = tmem + uint32_t(t & 1) * 128u;
+#pragma unroll
+                    for (int kk = 0; kk < kBlk / 16; ++kk) {
+                        const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
+                        umma_ts(tmem + 384u, a + acol, smem_desc_at(desc_mn, sK(st) + uint32_t(kk) * 2048u), idesc_dq,
+                                (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(BAR(B_KEMPTY + st));
+                };
+                if (ok) ok = issue_s(0);
+                if (ok) ok = issue_dp(0);
+                if (ok && T > 1) ok = issue_s(1);
+                for (int t = 0; t < T && ok; ++t) {
+                    ok = mbar_wait(BAR(B_DSFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 26);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (t + 1 < T) ok = issue_dp(t + 1);  // the dP columns are free once dS(t) is written
+                    if (!ok) break;
+                    issue_dq(t);
+                    if (t + 2 < T) ok = issue_s(t + 2);
+                }
+                if (ok) umma_commit(BAR(B_DONE));
+            }
+        }
+        __syncwarp();
+    } else {
+        setmaxnreg_inc<224>();
+        // ------------------------------ compute groups ------------------------------
+        const int w = warp >> 2;
+        const int r = tid & 127;
+        const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+        const int row = qb * kBlk + r;
+        const int cbase = 64 * w;
+        const float c = p.scale_log2;
+        const int64_t bh_ids = int64_t(b) * mk.He + he;
+        const int64_t bh_row = (int64_t(b) * p.H + h) * mk.L.Mpad + row;
+        const int qc = (mk.mode == 1) ? mk.plan[mk.L.off_qc + bh_ids * mk.L.Mpad + row] : 0;
+        const float lse = p.lse[bh_row];
+        const float delta = p.delta[bh_row];
+        bool ok = !aborted;
+
+        for (int t = 0; t < T && ok; ++t) {
+            const uint32_t entry = list[t];
+            const uint32_t fl = entry >> 10;
+            const int k0 = (lo + int(entry & 1023u)) * kBlk + cbase;  // first key column of this thread
+            const uint32_t tS = tmem + lane_base + uint32_t(t & 1) * 128u + uint32_t(cbase);
+            ok = mbar_wait(BAR(B_SFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 27);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[64];
+            tmem_ld32(tS, sr);
+            tmem_ld32(tS + 32u, sr + 32);
+            tc_wait_ld();
+            float* pr = reinterpret_cast<float*>(sr);
+#pragma unroll
+            for (int j = 0; j < 64; ++j) pr[j] = fast_exp2(fmaf(pr[j], c, -lse));
+            if (fl & (TILE_BOUND | TILE_DOC)) {
+                int lim = 63;
+                if (fl & TILE_BOUND) {
+                    int jmax = mk.N - 1;
+                    if (mk.causal) jmax = min(jmax, row + mk.gap);
+                    lim = jmax - k0;
+                }
+                if ((fl & TILE_DOC) && qc < 0) {
+                    const int4* kc4 = reinterpret_cast<const int4*>(mk.plan + mk.L.off_kc + bh_ids * mk.L.Npad + k0);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) {
+                        const int4 kc = __ldg(kc4 + q);
+                        pr[4 * q + 0] = (kc.x == qc && 4 * q + 0 <= lim) ? pr[4 * q + 0] : 0.f;
+                        pr[4 * q + 1] = (kc.y == qc && 4 * q + 1 <= lim) ? pr[4 * q + 1] : 0.f;
+                        pr[4 * q + 2] = (kc.z == qc && 4 * q + 2 <= lim) ? pr[4 * q + 2] : 0.f;
+                        pr[4 * q + 3] = (kc.w == qc && 4 * q + 3 <= lim) ? pr[4 * q + 3] : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) pr[j] = (j <= lim) ? pr[j] : 0.f;
+                }
+            }
+            ok = mbar_wait(BAR(B_DPFULL), t & 1, ab, ST_WAIT_TIMEOUT + 28);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t pk[32];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t dp[32];
+                tmem_ld32(tmem + lane_base + 256u + uint32_t(cbase) + uint32_t(q) * 32u, dp);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    // masked entries have P == 0 exactly, so dS is 0 there (flash_triton.py:400-414)
+                    const float d0 = pr[32 * q + 2 * j] * (__uint_as_float(dp[2 * j]) - delta);
+                    const float d1 = pr[32 * q + 2 * j + 1] * (__uint_as_float(dp[2 * j + 1]) - delta);
+                    pk[16 * q + j] = pack2<BF16>(pr[32 * q + 2 * j] == 0.f ? 0.f : d0,
+                                                 pr[32 * q + 2 * j + 1] == 0.f ? 0.f : d1);
+                }
+            }
+            tmem_st32(tS, pk);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(BAR(B_DSFULL + (t & 1)));
+        }
+
+        // ------------------------------ epilogue ------------------------------
+        if (ok && T > 0) ok = mbar_wait(BAR(B_DONE), 0, ab, ST_WAIT_TIMEOUT + 29);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok && misc[1] == 0) {
+            constexpr int HALF = D / 2;
+            const uint32_t c0 = uint32_t(w) * HALF;
+            uint8_t* orow = static_cast<uint8_t*>(p.dq.ptr) +
+                            2 * (int64_t(b) * p.dq.sb + int64_t(h) * p.dq.sh + int64_t(row) * p.dq.sl + c0);
+#pragma unroll
+            for (int q = 0; q < HALF / 32; ++q) {
+                uint32_t x[32];
+                tmem_ld32(tmem + lane_base + 384u + c0 + uint32_t(q) * 32u, x);
+                tc_wait_ld();
+                uint32_t out[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float v0 = (T > 0) ? __uint_as_float(x[2 * j]) * p.sm_scale : 0.f;
+                    const float v1 = (T > 0) ? __uint_as_float(x[2 * j + 1]) * p.sm_scale : 0.f;
+                    out[j] = pack2<BF16>(v0, v1);
+                }
+                if (row < mk.M) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + q * 64);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+template <int D, bool BF16>
+static cudaError_t launch_dq_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                               const CUtensorMap& tdo, const DqParams& p, int B, cudaStream_t stream) {
+    auto kern = bwd_dq_kernel<D, BF16>;
+    constexpr int smem = DqSmem<D>::total;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid(p.mask.L.nQ, p.H, B);
+    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_dq(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const CUtensorMap& tdo, const DqParams& p, int B, cudaStream_t stream) {
+    if (D == 128) return bf16 ? launch_dq_t<128, true>(tq, tk, tv, tdo, p, B, stream)
+                              : launch_dq_t<128, false>(tq, tk, tv, tdo, p, B, stream);
+    return bf16 ? launch_dq_t<64, true>(tq, tk, tv, tdo, p, B, stream)
+                : launch_dq_t<64, false>(tq, tk, tv, tdo, p, B, stream);
+}
+
+}  // namespace fa

@@ -1,0 +1,153 @@
+// Shared between the host API and all kernels: the mask-plan layout, the tile
+// classification and the per-entry keep predicate.
+//
+// Mask rule of the reference (flash_triton.py:103-116, :254, :270-282, :401-416):
+//   keep(i,j) = [j < N] & [!causal | (gap + i >= j)] & [mode != 1 | eq_i >= 0 | eq_i == ek_j]
+// with gap = max(0, N - M).
+#pragma once
+#include <stdint.h>
+#include "ptx.cuh"
+
+namespace fa {
+
+constexpr int kBlk = 128;  // rows of a query block = keys of a key block, for every kernel
+
+// Query code of an id >= 0 ("attends to everything"). Key codes are never positive.
+constexpr int32_t kCodeAny = 0x7fffffff;
+
+__host__ __device__ inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ inline int64_t pad128(int64_t x) { return (x + 127) / 128 * 128; }
+
+// Mask plan: one int32 array, sections in this order (all extents known from the problem).
+//   qc   [B, He, Mpad]  query codes: kCodeAny if eq >= 0, else eq itself (must fit in int32)
+//   kc   [B, He, Npad]  key codes: ek if -2^31 <= ek < 0, else 0 (can never equal a query code < 0)
+//   qmin, qmax [B, He, nQ]   min / max query code per block of 128 queries (valid rows only)
+//   kmin, kmax [B, He, nK]   min / max key code per block of 128 keys
+//   kv_lo, kv_hi [B, He, nQ] range of key blocks with an unmasked entry, per query block
+//   q_lo, q_hi   [B, He, nK] range of query blocks with an unmasked entry, per key block
+struct PlanLayout {
+    int B, He, M, N, nQ, nK;
+    int64_t Mpad, Npad;
+    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi;
+    int64_t total;  // int32 elements
+
+    __host__ __device__ PlanLayout() {}
+    __host__ __device__ PlanLayout(int B_, int He_, int M_, int N_) {
+        B = B_; He = He_; M = M_; N = N_;
+        nQ = cdiv(M, kBlk); nK = cdiv(N, kBlk);
+        Mpad = pad128(M); Npad = pad128(N);
+        int64_t bh = int64_t(B) * He;
+        int64_t o = 0;
+        off_qc = o;   o += bh * Mpad;
+        off_kc = o;   o += bh * Npad;
+        off_qmin = o; o += pad128(bh * nQ);
+        off_qmax = o; o += pad128(bh * nQ);
+        off_kmin = o; o += pad128(bh * nK);
+        off_kmax = o; o += pad128(bh * nK);
+        off_kvlo = o; o += pad128(bh * nQ);
+        off_kvhi = o; o += pad128(bh * nQ);
+        off_qlo = o;  o += pad128(bh * nK);
+        off_qhi = o;  o += pad128(bh * nK);
+        total = o;
+    }
+};
+
+// What every attention kernel needs to evaluate the mask.
+struct MaskArgs {
+    const int32_t* plan;  // null when mode == 0
+    PlanLayout L;
+    int M, N, gap, causal, mode;
+    int He;               // 1 or H
+};
+
+enum : uint32_t {
+    TILE_VISIT = 1u,   // at least one entry may be unmasked
+    TILE_BOUND = 2u,   // needs the per-entry j < N / causal check
+    TILE_DOC = 4u,     // needs the per-entry id check
+    TILE_QTAIL = 8u,   // holds rows >= M (matters to the backward kernels only)
+};
+
+// Classification of tile (qb, kb) from the block statistics. Conservative: a tile is skipped
+// only when every entry is masked, and declared free of a check only when every entry passes it.
+__host__ __device__ inline uint32_t classify_tile(int qb, int kb, int M, int N, int gap, int causal,
+                                                  int mode, int qmin, int qmax, int kmin, int kmax) {
+    const int q0 = qb * kBlk, k0 = kb * kBlk;
+    const int q1 = (q0 + kBlk < M) ? q0 + kBlk : M;  // exclusive
+    const int k1 = (k0 + kBlk < N) ? k0 + kBlk : N;
+    uint32_t f = TILE_VISIT;
+    if (k0 + kBlk > N) f |= TILE_BOUND;
+    if (q0 + kBlk > M) f |= TILE_QTAIL;
+    if (causal) {
+        if (k0 > q1 - 1 + gap) return 0;
+        if (k1 - 1 > q0 + gap) f |= TILE_BOUND;
+    }
+    if (mode == 1) {
+        if (qmax < 0 && (kmax < qmin || kmin > qmax)) return 0;
+        const bool all_any = (qmin >= 0);
+        const bool one_doc = (qmin == qmax) && (kmin == kmax) && (qmin == kmin);
+        if (!all_any && !one_doc) f |= TILE_DOC;
+    }
+    return f;
+}
+
+__device__ __forceinline__ uint32_t classify_from_plan(const MaskArgs& a, int b, int he, int qb, int kb) {
+    int qmin = 0, qmax = 0, kmin = 0, kmax = 0;
+    if (a.mode == 1) {
+        const int64_t bh = int64_t(b) * a.He + he;
+        qmin = a.plan[a.L.off_qmin + bh * a.L.nQ + qb];
+        qmax = a.plan[a.L.off_qmax + bh * a.L.nQ + qb];
+        kmin = a.plan[a.L.off_kmin + bh * a.L.nK + kb];
+        kmax = a.plan[a.L.off_kmax + bh * a.L.nK + kb];
+    }
+    return classify_tile(qb, kb, a.M, a.N, a.gap, a.causal, a.mode, qmin, qmax, kmin, kmax);
+}
+
+// Key-block range [lo, hi) a query block has to walk.
+__device__ __forceinline__ void kv_range(const MaskArgs& a, int b, int he, int qb, int& lo, int& hi) {
+    if (a.mode == 1) {
+        const int64_t bh = int64_t(b) * a.He + he;
+        lo = a.plan[a.L.off_kvlo + bh * a.L.nQ + qb];
+        hi = a.plan[a.L.off_kvhi + bh * a.L.nQ + qb];
+    } else {
+        lo = 0;
+        hi = a.L.nK;
+        if (a.causal) {
+            const int q1 = min(qb * kBlk + kBlk, a.M);
+            hi = min(a.L.nK, (q1 - 1 + a.gap) / kBlk + 1);
+        }
+    }
+}
+// Query-block range [lo, hi) a key block has to walk.
+__device__ __forceinline__ void q_range(const MaskArgs& a, int b, int he, int kb, int& lo, int& hi) {
+    if (a.mode == 1) {
+        const int64_t bh = int64_t(b) * a.He + he;
+        lo = a.plan[a.L.off_qlo + bh * a.L.nK + kb];
+        hi = a.plan[a.L.off_qhi + bh * a.L.nK + kb];
+    } else {
+        lo = 0;
+        hi = a.L.nQ;
+        if (a.causal) {
+            const int first = kb * kBlk - a.gap;  // first query row that sees key k0
+            lo = first > 0 ? first / kBlk : 0;
+            if (lo > hi) lo = hi;
+        }
+    }
+}
+
+// The per-entry predicate on codes. Identical to the reference's rule on the original ids:
+// qc >= 0 <=> eq >= 0; for eq < 0, qc == eq and kc == ek whenever ek is a negative int32,
+// and kc == 0 != qc otherwise.
+__device__ __forceinline__ bool keep_entry(int i, int j, int qc, int kc, int N, int gap, int causal, int mode) {
+    bool keep = j < N;
+    if (causal) keep = keep && (gap + i >= j);
+    if (mode == 1) keep = keep && ((qc >= 0) || (qc == kc));
+    return keep;
+}
+
+// Device-side view of a [B, H, L, D] tensor for plain (non-TMA) stores.
+struct OutTensor {
+    void* ptr;
+    int64_t sb, sh, sl;  // element strides; the D stride is 1
+};
+
+}  // namespace fa

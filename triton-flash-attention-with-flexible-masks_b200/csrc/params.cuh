@@ -1,0 +1,64 @@
+// Kernel parameter blocks, filled by api.cu.
+#pragma once
+#include "common.cuh"
+
+namespace fa {
+
+constexpr int kAttnThreads = 384;  // 3 warpgroups: two compute groups, one producer / MMA group
+constexpr int kFwdThreads = kAttnThreads;
+constexpr int kListCap = 1024;     // blocks per sequence (visited-tile lists live in shared memory)
+
+struct FwdParams {
+    OutTensor o;
+    float* lse;  // [B, H, Mpad], log2 domain
+    MaskArgs mask;
+    int H, G;
+    float scale_log2;  // sm_scale * log2(e)
+    int* status;
+};
+
+struct DeltaParams {
+    OutTensor o, d_o;
+    float* delta;  // [B, H, Mpad]
+    int B, H, M, D;
+    int64_t Mpad;
+    bool bf16;
+};
+
+struct DkdvParams {
+    OutTensor dk, dv;    // [B, Hk, N, D]
+    const float* lse;    // [B, H, Mpad]
+    const float* delta;  // [B, H, Mpad]
+    MaskArgs mask;
+    int H, Hk, G;
+    float scale_log2, sm_scale;
+    int* status;
+};
+
+struct DqParams {
+    OutTensor dq;        // [B, H, M, D]
+    const float* lse;
+    const float* delta;
+    MaskArgs mask;
+    int H, G;
+    float scale_log2, sm_scale;
+    int* status;
+};
+
+// Ordered compaction of per-tile flags (list[i] = flags of tile lo+i) into the visited list:
+// entry = (i) | flags << 10. One warp; returns the number of visited tiles.
+__device__ __forceinline__ int compact_visit_list(uint16_t* list, int n, int lane) {
+    int T = 0;
+    for (int base = 0; base < n; base += 32) {
+        const int i = base + lane;
+        const uint32_t f = (i < n) ? list[i] : 0u;
+        const uint32_t m = __ballot_sync(0xffffffffu, (f & TILE_VISIT) != 0);
+        __syncwarp();
+        if (f & TILE_VISIT) list[T + __popc(m & ((1u << lane) - 1u))] = uint16_t(uint32_t(i) | (f << 10));
+        T += __popc(m);
+        __syncwarp();
+    }
+    return T;
+}
+
+}  // namespace fa

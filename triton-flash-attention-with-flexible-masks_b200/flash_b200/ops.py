@@ -1,0 +1,248 @@
+"""Host-side mirror of the reference operator (flash_triton.py:506-641).
+
+`attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)` keeps the reference's
+signature, defaults, assertions, saved-tensor contract and return convention; the four Triton
+launches are replaced by calls into libfa_b200.so (hand-written sm_100a kernels). There is no
+Triton, no dispatch over back-ends and no CPU path: CPU tensors raise.
+"""
+import ctypes
+import math
+import os
+
+import torch
+
+from . import _lib
+
+# scoring function modes (flash_triton.py:18-22)
+SCORE_FUNC_MODE0_NOPE = 0  # no extra mask
+SCORE_FUNC_MODE1_DOC = 1   # query id < 0: attend only to keys with the same id; id >= 0: attend to all
+
+_DTYPES = {torch.bfloat16: _lib.FA_BF16, torch.float16: _lib.FA_FP16}
+_STATUS = {}  # device index -> int32[1] status word
+_SYNC_STATUS = os.environ.get("FA_B200_SYNC_STATUS", "0") not in ("", "0")
+
+
+def _status_word(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _STATUS.get(idx)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[idx] = st
+    return st
+
+
+def check_status(device=None):
+    """Synchronises `device` and raises if a kernel recorded an error since the last check."""
+    devs = list(_STATUS) if device is None else [torch.device(device).index or 0]
+    for idx in devs:
+        st = _STATUS.get(idx)
+        if st is None:
+            continue
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            if 100 <= code < 200:
+                raise RuntimeError(f"flash_b200: a bounded wait inside a kernel ran out (role {code - 100}); "
+                                   "results of that call are invalid")
+            if code == 200:
+                raise RuntimeError("flash_b200: a negative query id does not fit in int32")
+            raise RuntimeError(f"flash_b200: kernel status {code}")
+
+
+def maybe_contiguous(x):
+    """flash_triton.py:435-437, extended by the TMA rules: last stride 1, 16-byte aligned base,
+    other strides positive multiples of 8 elements."""
+    ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+    if ok:
+        for size, stride in zip(x.shape[:-1], x.stride()[:-1]):
+            if size > 1 and (stride <= 0 or stride % 8 != 0):
+                ok = False
+    return x if ok else x.contiguous()
+
+
+def _tensor(x):
+    t = _lib.Tensor()
+    t.ptr = x.data_ptr()
+    for i in range(4):
+        t.stride[i] = x.stride(i)
+    return t
+
+
+def _ids(x):
+    i = _lib.Ids()
+    i.ptr = x.data_ptr()
+    for d in range(3):
+        i.stride[d] = x.stride(d)
+    i.dtype = _lib.FA_ID_INT32 if x.dtype == torch.int32 else _lib.FA_ID_INT64
+    return i
+
+
+def _id_tensor(e, B, H, L, name):
+    assert e.dim() == 3 and e.shape[0] == B and e.shape[1] == H and e.shape[2] == L, \
+        f"{name} must have shape [bs, H, L] = {[B, H, L]}, got {list(e.shape)}"
+    assert not e.dtype.is_floating_point and not e.dtype.is_complex, f"{name} must hold integer ids"
+    if e.dtype not in (torch.int32, torch.int64):
+        e = e.to(torch.int64)
+    return e
+
+
+def _problem(B, H, Hk, M, N, D, dtype, causal, mode, id_heads, sm_scale):
+    p = _lib.Problem()
+    p.B, p.H, p.Hk, p.M, p.N, p.D = B, H, Hk, M, N, D
+    if dtype not in _DTYPES:
+        raise NotImplementedError(f"flash_b200 supports bf16 and fp16 inputs, got {dtype}")
+    p.dtype = _DTYPES[dtype]
+    p.causal = 1 if causal else 0
+    p.mode = int(mode)
+    p.id_heads = id_heads
+    p.sm_scale = float(sm_scale)
+    return p
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def build_plan(prob, eq, ek, status):
+    """Mask plan for (eq, ek): int32 device buffer consumed by the forward and backward kernels."""
+    lib = _lib.load()
+    nbytes = ctypes.c_size_t(0)
+    _lib.check(lib.fa_plan_bytes(ctypes.byref(prob), ctypes.byref(nbytes)), "fa_plan_bytes")
+    plan = torch.empty(max(nbytes.value // 4, 1), dtype=torch.int32, device=eq.device)
+    ieq, iek = _ids(eq), _ids(ek)
+    _lib.check(lib.fa_plan_build(ctypes.byref(prob), ctypes.byref(ieq), ctypes.byref(iek), plan.data_ptr(),
+                                 nbytes.value, status.data_ptr(), _stream()), "fa_plan_build")
+    return plan
+
+
+class FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, eq, ek, score_func_mode):
+        lib = _lib.load()
+        # checks of flash_triton.py:510-520
+        Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+        assert Dq == Dk and Dk == Dv, "feature size of q, k, v should be equal"
+        assert Dk in {16, 32, 64, 128}
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        Hk, Hv = k.shape[1], v.shape[1]
+        assert Hk == Hv, "num of heads in k and v should be equal"
+        assert H % Hk == 0, "number of heads in q must be a multiple of that in k & v"
+        num_groups = H // Hk
+        assert (N >= M) or (not causal), "KV length should be larger than M length in causal mode!"
+        MN_GAP = max(0, N - M)
+        if not q.is_cuda:
+            raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+        if D not in (64, 128):
+            raise NotImplementedError(f"flash_b200 implements head dims 64 and 128, got {D}")
+        if sm_scale is None:
+            sm_scale = 1. / math.sqrt(D)
+        if not sm_scale > 0:
+            raise NotImplementedError("flash_b200 needs sm_scale > 0")
+        q, k, v = maybe_contiguous(q), maybe_contiguous(k), maybe_contiguous(v)
+        # score mode (flash_triton.py:527-530)
+        assert (eq is None) == (ek is None)
+        if eq is None:
+            assert score_func_mode == SCORE_FUNC_MODE0_NOPE
+        assert score_func_mode in (SCORE_FUNC_MODE0_NOPE, SCORE_FUNC_MODE1_DOC)
+        id_heads = 1
+        if score_func_mode == SCORE_FUNC_MODE1_DOC:
+            eq = _id_tensor(eq, B, H, M, "eq")
+            ek = _id_tensor(ek, B, H, N, "ek")
+            broadcast = (H == 1) or (eq.stride(1) == 0 and ek.stride(1) == 0)
+            id_heads = 1 if broadcast else H
+        with torch.cuda.device(q.device):
+            prob = _problem(B, H, Hk, M, N, D, q.dtype, causal, score_func_mode, id_heads, sm_scale)
+            status = _status_word(q.device)
+            plan = None
+            if score_func_mode == SCORE_FUNC_MODE1_DOC:
+                plan = build_plan(prob, eq, ek, status)
+            Out = torch.empty_like(q)
+            if maybe_contiguous(Out) is not Out:
+                Out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            Mpad = lib.fa_padded_rows(M)
+            L = torch.empty((B, H, Mpad), device=q.device, dtype=torch.float32)
+            tq, tk, tv, to = _tensor(q), _tensor(k), _tensor(v), _tensor(Out)
+            _lib.check(lib.fa_fwd(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                  ctypes.byref(to), L.data_ptr(), plan.data_ptr() if plan is not None else None,
+                                  status.data_ptr(), _stream()), "fa_fwd")
+            if _SYNC_STATUS:
+                check_status(q.device)
+        # autograd context (flash_triton.py:558-562); eq/ek are kept for the saved-tensor contract,
+        # the plan built from them is reused by backward
+        if eq is None:
+            ctx.save_for_backward(q, k, v, Out, L)
+        else:
+            ctx.save_for_backward(q, k, v, Out, L, eq, ek)
+        ctx.plan = plan
+        ctx.id_heads = id_heads
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        ctx.shapes = (B, H, M, D, N, Hk, num_groups, MN_GAP)
+        ctx.score_func_info = (score_func_mode, )
+        return Out
+
+    @staticmethod
+    def backward(ctx, do):
+        lib = _lib.load()
+        q, k, v, o, L = ctx.saved_tensors[:5]
+        sm_scale = ctx.sm_scale
+        causal = ctx.causal
+        B, H, M, D, N, Hk, num_groups, MN_GAP = ctx.shapes
+        score_func_mode, = ctx.score_func_info
+        plan = ctx.plan
+        do = maybe_contiguous(do)
+        with torch.cuda.device(q.device):
+            prob = _problem(B, H, Hk, M, N, D, q.dtype, causal, score_func_mode, ctx.id_heads, sm_scale)
+            status = _status_word(q.device)
+            stream = _stream()
+            plan_ptr = plan.data_ptr() if plan is not None else None
+            tq, tk, tv, to, tdo = _tensor(q), _tensor(k), _tensor(v), _tensor(o), _tensor(do)
+            # delta = rowsum(o * do) (flash_triton.py:584-592)
+            delta = torch.empty_like(L)
+            _lib.check(lib.fa_bwd_delta(ctypes.byref(prob), ctypes.byref(to), ctypes.byref(tdo), delta.data_ptr(),
+                                        stream), "fa_bwd_delta")
+            # dk, dv (flash_triton.py:594-614, group sum of :635-637 done inside the kernel)
+            dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
+            dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=q.device)
+            tdk, tdv = _tensor(dk), _tensor(dv)
+            _lib.check(lib.fa_bwd_dkdv(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                       ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdk),
+                                       ctypes.byref(tdv), plan_ptr, status.data_ptr(), stream), "fa_bwd_dkdv")
+            # dq (flash_triton.py:616-634); every row is written by the kernel
+            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            tdq = _tensor(dq)
+            _lib.check(lib.fa_bwd_dq(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                     ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdq), plan_ptr,
+                                     status.data_ptr(), stream), "fa_bwd_dq")
+            if _SYNC_STATUS:
+                check_status(q.device)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
+    """Drop-in for flash_triton.py:640-641."""
+    return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
+
+
+def debug_mask(B, H, M, N, causal, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE, device="cuda"):
+    """Materialises the kernels' keep / tile-class decisions: returns (keep [B,He,M,N] bool,
+    tile_class [B,He,nQ,nK] uint8) computed on the device by the attention kernels' own predicate."""
+    lib = _lib.load()
+    device = torch.device(device)
+    id_heads = 1
+    with torch.cuda.device(device):
+        status = _status_word(device)
+        if score_func_mode == SCORE_FUNC_MODE1_DOC:
+            eq = _id_tensor(eq, B, H, M, "eq")
+            ek = _id_tensor(ek, B, H, N, "ek")
+            id_heads = 1 if (H == 1 or (eq.stride(1) == 0 and ek.stride(1) == 0)) else H
+        prob = _problem(B, H, H, M, N, 64, torch.bfloat16, causal, score_func_mode, id_heads, 1.0)
+        plan = build_plan(prob, eq, ek, status) if score_func_mode == SCORE_FUNC_MODE1_DOC else None
+        He = id_heads if score_func_mode == SCORE_FUNC_MODE1_DOC else 1
+        nQ, nK = (M + 127) // 128, (N + 127) // 128
+        keep = torch.zeros((B, He, M, N), dtype=torch.uint8, device=device)
+        cls = torch.zeros((B, He, nQ, nK), dtype=torch.uint8, device=device)
+        _lib.check(lib.fa_debug_mask(ctypes.byref(prob), plan.data_ptr() if plan is not None else None,
+                                     keep.data_ptr(), cls.data_ptr(), _stream()), "fa_debug_mask")
+    return keep.bool(), cls
