@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the document-masked attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3]
+
+One "step" is one forward + backward pass of `attention()` over the workload. The default
+workload is benchmark configuration 3: doc-masked causal bf16 attention, bs=1, H=32, L=32768,
+D=128, 64 documents with lognormal lengths (seeded synthetic inputs). With N > 1 (launched by
+torchrun, one process per GPU) the 32 heads are split over the ranks, with no communication in
+the operator; the step time is the maximum over ranks. The metric is effective TFLOP/s:
+14 * D * nnz per step, nnz = number of unmasked score entries (4*D*nnz forward, 10*D*nnz backward).
+
+`--impl reference` times the reference's CPU masked-attention computation (its restatement in
+oracle/attention_oracle.py, fp32 torch on the host cores) on a bounded sample of the same workload.
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "triton-flash-attention-with-flexible-masks_b200"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import numpy as np
+import torch
+
+import workloads
+
+METRIC = "effective attention TFLOP/s fwd+bwd (doc-masked bf16)"
+# algorithmic FLOPs per unmasked entry, in units of D: S and P*V forward; S, dP, dV, dK in the
+# dK/dV kernel; dQ (the dQ kernel's recomputation of S and dP is not algorithmic work)
+FLOPS_PER_ENTRY = {"fwd": 4, "dkdv": 8, "dq": 2}
+L2_FLUSH_BYTES = 256 << 20
+
+
+def nnz_per_head(w):
+    """Exact unmasked-entry count of one head, per batch entry (ids are head-broadcast)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from attention_oracle import count_unmasked  # integer bookkeeping only
+    cfg = w["cfg"]
+    return [count_unmasked(cfg["M"], cfg["N"], w["causal"],
+                           None if w["eq_np"] is None else w["eq_np"][b],
+                           None if w["ek_np"] is None else w["ek_np"][b], w["mode"]) for b in range(cfg["B"])]
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs
+    (read-only queries)."""
+
+    def __init__(self, device_index):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(device_index).uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------
+# CPU leg: the reference's masked-attention computation on the host cores, bounded sample
+# ------------------------------------------------------------------------------------------
+def cpu_sample(name, steps=1, warmup=0, rows=2048):
+    """Times forward+backward of the LAST `rows` queries of one head against all keys they can
+    see (the longest rows of the causal workload), fp32, all host threads."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import attention_oracle as orc
+    cfg = workloads.CONFIGS[name]
+    M, N, D = cfg["M"], cfg["N"], cfg["D"]
+    rng = np.random.default_rng(workloads.SEEDS[name])
+    eq_np, ek_np = workloads.doc_ids(name, rng, B=1)
+    g = torch.Generator().manual_seed(workloads.SEEDS[name])
+    rows = min(rows, M)
+    q = torch.randn(rows, D, generator=g) * cfg["std"]
+    k = torch.randn(N, D, generator=g) * cfg["std"]
+    v = torch.randn(N, D, generator=g) * cfg["std"]
+    do = torch.randn(rows, D, generator=g) * cfg["std"]
+    eq = torch.from_numpy(eq_np[0][M - rows:]) if eq_np is not None else None
+    ek = torch.from_numpy(ek_np[0]) if ek_np is not None else None
+    # rows M-rows..M-1 of an M x N causal problem == a rows x N problem with the same bottom-right alignment
+    nnz = orc.count_unmasked(rows, N, cfg["causal"], None if eq is None else eq.numpy(),
+                             None if ek is None else ek.numpy(), cfg["mode"])
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.attention_one_head_chunked(q, k, v, do, cfg["causal"], 1.0 / np.sqrt(D), eq, ek, cfg["mode"], chunk=512)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    sec = float(np.mean(times))
+    flops = 14.0 * D * nnz
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{name}: last {rows} query rows of one head x all {N} keys, fwd+bwd, fp32 torch on CPU, "
+                      f"{sec * 1e3:.0f} ms per pass, nnz={nnz}",
+            "ms_per_step": sec * 1e3}
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    r = cpu_sample(args.workload, steps=args.steps, warmup=args.warmup)
+    cfg = workloads.CONFIGS[args.workload]
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args.workload, cfg), "sample": r["sample"]},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(name, cfg):
+    return (f"{name}: doc-masked={'yes' if cfg['mode'] else 'no'} causal={cfg['causal']} {cfg['dtype']} "
+            f"bs={cfg['B']} H={cfg['H']} Lq={cfg['M']} Lk={cfg['N']} D={cfg['D']}")
+
+
+# ------------------------------------------------------------------------------------------
+# GPU leg
+# ------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    import flash_b200 as fb
+    from flash_b200 import ops, shard
+
+    rank, world, local = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    name = args.workload
+    cfg = workloads.CONFIGS[name]
+    dim, qs, _ = shard.shard_slices(cfg["B"], cfg["H"], cfg["Hk"], world, rank)
+    n_local = len(range(*qs.indices(cfg["H"] if dim == 1 else cfg["B"])))
+    kw = {"H": n_local} if dim == 1 else {"B": n_local}
+    w = workloads.make_inputs(name, device=dev, **kw)          # this rank's shard, same ids on every rank
+    per_b = nnz_per_head(w)
+    # equal shards with the same ids on every rank
+    nnz_local = sum(per_b) * (n_local if dim == 1 else cfg["H"])
+    nnz_total = nnz_local * world
+    D = cfg["D"]
+    backward = not args.forward_only and w["do"] is not None
+    flops_step_local = (14.0 if backward else 4.0) * D * nnz_local
+    flops_step_total = flops_step_local * world  # equal shards
+
+    q, k, v = [w[x].requires_grad_(backward) for x in "qkv"]
+    att = (w["causal"], w["sm_scale"], w["eq"], w["ek"], w["mode"])
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device=dev)
+
+    def step():
+        o = fb.attention(q, k, v, *att)
+        if backward:
+            o.backward(w["do"])
+            q.grad = k.grad = v.grad = None
+        return o
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ops.PROFILE = []
+    launches0 = ops.LAUNCHES
+    evs = []
+    for _ in range(args.steps):
+        flush.zero_()  # L2 flush between timed iterations (not timed)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        evs.append((e0, e1))
+    barrier()
+    clocks = sampler.stop()
+    prof, ops.PROFILE = ops.PROFILE, None
+    launches = ops.LAUNCHES - launches0
+    fb.check_status()
+    total_ms = sum(a.elapsed_time(b) for a, b in evs)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = flops_step_total / (ms_per_step * 1e-3) / 1e12
+
+    # per-kernel durations measured live in the timed region (events on the launching stream)
+    kern = {}
+    for nm, a, b in prof:
+        kern.setdefault(nm, []).append(a.elapsed_time(b))
+    kern_ms = {nm: float(np.mean(x)) for nm, x in kern.items()}
+    peak_tf, peak_bw, peak_src = peaks()
+    dom = max((nm for nm in kern_ms if nm in FLOPS_PER_ENTRY), key=lambda nm: kern_ms[nm])
+    achieved = FLOPS_PER_ENTRY[dom] * D * nnz_local / (kern_ms[dom] * 1e-3) / 1e12
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get(f"{name}:{dom}:n{world}")
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                "frac": achieved / peak_tf, "traffic": traffic, "peak_source": peak_src + " (cuBLAS bf16 burst)",
+                "frac_of_nominal_2250": achieved / 2250.0,
+                "kernel_ms": kern_ms,
+                "per_kernel_tflops": {nm: FLOPS_PER_ENTRY[nm] * D * nnz_local / (kern_ms[nm] * 1e-3) / 1e12
+                                      for nm in kern_ms if nm in FLOPS_PER_ENTRY}}
+
+    # end to end through the public call with HOST buffers: H2D of q, k, v, dO and ids from pinned
+    # memory, forward + backward, D2H of O, dQ, dK, dV -- all inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        host_in = {x: w[x].detach().cpu().pin_memory() for x in (("q", "k", "v", "do") if backward else ("q", "k", "v"))}
+        ids_host = None
+        if w["eq"] is not None:
+            ids_host = (w["eq"][:, :1].contiguous().cpu().pin_memory(), w["ek"][:, :1].contiguous().cpu().pin_memory())
+        outs = ("o", "dq", "dk", "dv") if backward else ("o",)
+        host_out = {x: torch.empty(w["q" if x in ("o", "dq") else "k"].shape, dtype=w["q"].dtype).pin_memory() for x in outs}
+        h2d = sum(t_.numel() * t_.element_size() for t_ in host_in.values())
+        if ids_host:
+            h2d += sum(t_.numel() * t_.element_size() for t_ in ids_host)
+        d2h = sum(t_.numel() * t_.element_size() for t_ in host_out.values())
+
+        def e2e_step():
+            dq_, dk_, dv_ = [host_in[x].to(dev, non_blocking=True).requires_grad_(backward) for x in "qkv"]
+            eq_ = ek_ = None
+            if ids_host:
+                eq_ = ids_host[0].to(dev, non_blocking=True).expand(w["eq"].shape)
+                ek_ = ids_host[1].to(dev, non_blocking=True).expand(w["ek"].shape)
+            o = fb.attention(dq_, dk_, dv_, w["causal"], w["sm_scale"], eq_, ek_, w["mode"])
+            host_out["o"].copy_(o.detach(), non_blocking=True)
+            if backward:
+                o.backward(host_in["do"].to(dev, non_blocking=True))
+                host_out["dq"].copy_(dq_.grad, non_blocking=True)
+                host_out["dk"].copy_(dk_.grad, non_blocking=True)
+                host_out["dv"].copy_(dv_.grad, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 5))
+        e2e_step()
+        barrier()
+        ev = []
+        for _ in range(n_e2e):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            e2e_step()
+            e1.record()
+            ev.append((e0, e1))
+        barrier()
+        ms = sum(a.elapsed_time(b) for a, b in ev) / n_e2e
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        e2e = {"value": flops_step_total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+               "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world, "steps": n_e2e}
+        fb.check_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_sample(name)
+        cpu = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        dense = cfg["B"] * cfg["H"] * cfg["M"] * cfg["N"] * (0.5 if cfg["causal"] else 1.0)
+        line = {"metric": METRIC if backward else METRIC.replace("fwd+bwd", "fwd"), "value": value, "unit": "TFLOP/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"],
+                "data": "synthetic",
+                "config": {"workload": workload_name(name, cfg), "seed": workloads.SEEDS[name],
+                           "sharding": f"{'heads' if dim == 1 else 'batches'} over {world} rank(s), {n_local} per rank",
+                           "l2": "256 MiB buffer written between timed iterations",
+                           "unmasked_fraction_of_causal": nnz_total / dense,
+                           "dense_count_tflops": (14.0 if backward else 4.0) * D * dense / (ms_per_step * 1e-3) / 1e12},
+                "frac_of_measured_peak": value / (peak_tf * world), "frac_of_nominal_peak": value / (2250.0 * world),
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=list(workloads.CONFIGS))
+    ap.add_argument("--forward-only", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

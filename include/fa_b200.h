@@ -107,6 +107,13 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
  * bit2 id check, bit3 query tail. Either pointer may be NULL. */
 int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream);
 
+/* Host-only helper, no GPU involved: the tile classification the kernels apply to tile
+ * (qb, kb) given the id-code min/max of its query block and key block. Returns the tile_class
+ * bits of fa_debug_mask. Exposed so that the block-skipping rule can be tested on a CPU
+ * (no counterpart in the reference, which never skips a tile). */
+uint32_t fa_classify_tile(int32_t M, int32_t N, int32_t causal, int32_t mode, int32_t qb, int32_t kb,
+                          int32_t qmin, int32_t qmax, int32_t kmin, int32_t kmax);
+
 #ifdef __cplusplus
 }
 #endif

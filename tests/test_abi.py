@@ -1,0 +1,95 @@
+"""CPU tests of the C ABI: the library loads without a GPU, exports every declared symbol, and
+rejects bad problems before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from flash_b200 import _lib
+
+
+def _declared(repo_root):
+    text = open(os.path.join(repo_root, "include", "fa_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fa_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(repo_root):
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared(repo_root)
+    assert len(names) >= 11
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/fa_b200.h but not exported"
+    assert set(_lib.EXPORTS) <= set(names)
+
+
+def test_no_link_dependency_on_the_driver():
+    import subprocess
+    out = subprocess.run(["ldd", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    assert "libcuda.so" not in out and "libcudart" not in out and "libtorch" not in out
+
+
+def test_version_and_strings():
+    lib = _lib.load()
+    assert lib.fa_version() == 1
+    assert lib.fa_error_string(0) == b"ok"
+    assert b"TMA" in lib.fa_error_string(3)
+    assert lib.fa_padded_rows(1) == 128 and lib.fa_padded_rows(128) == 128 and lib.fa_padded_rows(129) == 256
+
+
+def _prob(**kw):
+    p = _lib.Problem()
+    base = dict(B=1, H=2, Hk=2, M=256, N=256, D=128, dtype=0, causal=1, mode=1, id_heads=1, sm_scale=0.1)
+    base.update(kw)
+    for k, v in base.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_plan_bytes():
+    lib = _lib.load()
+    n = ctypes.c_size_t(0)
+    assert lib.fa_plan_bytes(ctypes.byref(_prob()), ctypes.byref(n)) == 0
+    # codes for 256 queries + 256 keys, plus eight per-block arrays padded to 128 entries
+    assert n.value == 4 * (256 + 256 + 8 * 128)
+    assert lib.fa_plan_bytes(ctypes.byref(_prob(mode=0)), ctypes.byref(n)) == 0 and n.value == 0
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(D=32), 2), (dict(D=256), 2), (dict(dtype=5), 2), (dict(sm_scale=0.0), 2), (dict(sm_scale=-1.0), 2),
+    (dict(H=3, Hk=2), 1), (dict(M=0), 1), (dict(mode=7), 1), (dict(M=512, N=256, causal=1), 1),
+    (dict(id_heads=3), 1), (dict(N=128 * 1024 + 1, M=128), 2),
+])
+def test_bad_problems_are_refused(kw, code):
+    lib = _lib.load()
+    n = ctypes.c_size_t(0)
+    assert lib.fa_plan_bytes(ctypes.byref(_prob(**kw)), ctypes.byref(n)) == code
+
+
+def test_forward_refuses_bad_tensors_without_a_gpu():
+    lib = _lib.load()
+    t = _lib.Tensor()
+    t.ptr = 0
+    p = _prob(mode=0)
+    st = ctypes.c_int32(0)
+    lse = (ctypes.c_float * 4)()
+    rc = lib.fa_fwd(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t),
+                    ctypes.cast(lse, ctypes.c_void_p), None, ctypes.cast(ctypes.pointer(st), ctypes.c_void_p), None)
+    assert rc == 1  # null tensor pointer
+    t.ptr = 0x1008  # misaligned
+    for i, s in enumerate((1 << 20, 1 << 16, 128, 1)):
+        t.stride[i] = s
+    rc = lib.fa_fwd(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t),
+                    ctypes.cast(lse, ctypes.c_void_p), None, ctypes.cast(ctypes.pointer(st), ctypes.c_void_p), None)
+    assert rc == 3
+    t.ptr = 0x1000
+    t.stride[2] = 100  # row stride not a multiple of 8 elements
+    rc = lib.fa_fwd(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t),
+                    ctypes.cast(lse, ctypes.c_void_p), None, ctypes.cast(ctypes.pointer(st), ctypes.c_void_p), None)
+    assert rc == 3
+    # document mode without a plan
+    t.stride[2] = 128
+    rc = lib.fa_fwd(ctypes.byref(_prob()), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t),
+                    ctypes.cast(lse, ctypes.c_void_p), None, ctypes.cast(ctypes.pointer(st), ctypes.c_void_p), None)
+    assert rc == 6

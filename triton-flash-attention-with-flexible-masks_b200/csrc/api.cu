@@ -267,6 +267,12 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
 }
 
+uint32_t fa_classify_tile(int32_t M, int32_t N, int32_t causal, int32_t mode, int32_t qb, int32_t kb, int32_t qmin,
+                          int32_t qmax, int32_t kmin, int32_t kmax) {
+    const int gap = N > M ? N - M : 0;
+    return fa::classify_tile(qb, kb, M, N, gap, causal ? 1 : 0, mode, qmin, qmax, kmin, kmax);
+}
+
 int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream) {
     int rc = check_problem(p);
     if (rc) return rc;

@@ -13,7 +13,7 @@ FA_ID_NONE, FA_ID_INT32, FA_ID_INT64 = 0, 1, 2
 
 EXPORTS = (
     "fa_version", "fa_error_string", "fa_padded_rows", "fa_plan_bytes", "fa_plan_build", "fa_fwd",
-    "fa_bwd_delta", "fa_bwd_dkdv", "fa_bwd_dq", "fa_debug_mask",
+    "fa_bwd_delta", "fa_bwd_dkdv", "fa_bwd_dq", "fa_debug_mask", "fa_classify_tile",
 )
 
 
@@ -68,6 +68,8 @@ def load():
     lib.fa_bwd_dq.argtypes = [P, T, T, T, T, vp, vp, T, vp, vp, vp]
     lib.fa_debug_mask.restype = i32
     lib.fa_debug_mask.argtypes = [P, vp, vp, vp, vp]
+    lib.fa_classify_tile.restype = ctypes.c_uint32
+    lib.fa_classify_tile.argtypes = [ctypes.c_int32] * 10
     _lib = lib
     return lib
 

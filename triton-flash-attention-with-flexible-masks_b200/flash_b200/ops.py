@@ -20,6 +20,32 @@ SCORE_FUNC_MODE1_DOC = 1   # query id < 0: attend only to keys with the same id;
 _DTYPES = {torch.bfloat16: _lib.FA_BF16, torch.float16: _lib.FA_FP16}
 _STATUS = {}  # device index -> int32[1] status word
 _SYNC_STATUS = os.environ.get("FA_B200_SYNC_STATUS", "0") not in ("", "0")
+# When set to a list, every kernel launch appends (name, start_event, end_event) recorded on the
+# launching stream, and LAUNCHES counts the library's kernels. Used by the benchmark only.
+PROFILE = None
+LAUNCHES = 0
+
+
+class _Timed:
+    """Brackets one C-ABI call with CUDA events on the current stream when PROFILE is a list."""
+
+    def __init__(self, name, kernels=1):
+        self.name, self.kernels = name, kernels
+
+    def __enter__(self):
+        global LAUNCHES
+        LAUNCHES += self.kernels
+        if PROFILE is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if PROFILE is not None:
+            self.e1.record()
+            PROFILE.append((self.name, self.e0, self.e1))
+        return False
 
 
 def _status_word(device):
@@ -110,8 +136,9 @@ def build_plan(prob, eq, ek, status):
     _lib.check(lib.fa_plan_bytes(ctypes.byref(prob), ctypes.byref(nbytes)), "fa_plan_bytes")
     plan = torch.empty(max(nbytes.value // 4, 1), dtype=torch.int32, device=eq.device)
     ieq, iek = _ids(eq), _ids(ek)
-    _lib.check(lib.fa_plan_build(ctypes.byref(prob), ctypes.byref(ieq), ctypes.byref(iek), plan.data_ptr(),
-                                 nbytes.value, status.data_ptr(), _stream()), "fa_plan_build")
+    with _Timed("plan", 2):
+        _lib.check(lib.fa_plan_build(ctypes.byref(prob), ctypes.byref(ieq), ctypes.byref(iek), plan.data_ptr(),
+                                     nbytes.value, status.data_ptr(), _stream()), "fa_plan_build")
     return plan
 
 
@@ -131,6 +158,11 @@ class FlashAttention(torch.autograd.Function):
         num_groups = H // Hk
         assert (N >= M) or (not causal), "KV length should be larger than M length in causal mode!"
         MN_GAP = max(0, N - M)
+        # score mode (flash_triton.py:527-530)
+        assert (eq is None) == (ek is None)
+        if eq is None:
+            assert score_func_mode == SCORE_FUNC_MODE0_NOPE
+        assert score_func_mode in (SCORE_FUNC_MODE0_NOPE, SCORE_FUNC_MODE1_DOC)
         if not q.is_cuda:
             raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
         if D not in (64, 128):
@@ -140,11 +172,6 @@ class FlashAttention(torch.autograd.Function):
         if not sm_scale > 0:
             raise NotImplementedError("flash_b200 needs sm_scale > 0")
         q, k, v = maybe_contiguous(q), maybe_contiguous(k), maybe_contiguous(v)
-        # score mode (flash_triton.py:527-530)
-        assert (eq is None) == (ek is None)
-        if eq is None:
-            assert score_func_mode == SCORE_FUNC_MODE0_NOPE
-        assert score_func_mode in (SCORE_FUNC_MODE0_NOPE, SCORE_FUNC_MODE1_DOC)
         id_heads = 1
         if score_func_mode == SCORE_FUNC_MODE1_DOC:
             eq = _id_tensor(eq, B, H, M, "eq")
@@ -163,9 +190,10 @@ class FlashAttention(torch.autograd.Function):
             Mpad = lib.fa_padded_rows(M)
             L = torch.empty((B, H, Mpad), device=q.device, dtype=torch.float32)
             tq, tk, tv, to = _tensor(q), _tensor(k), _tensor(v), _tensor(Out)
-            _lib.check(lib.fa_fwd(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
-                                  ctypes.byref(to), L.data_ptr(), plan.data_ptr() if plan is not None else None,
-                                  status.data_ptr(), _stream()), "fa_fwd")
+            with _Timed("fwd"):
+                _lib.check(lib.fa_fwd(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                      ctypes.byref(to), L.data_ptr(), plan.data_ptr() if plan is not None else None,
+                                      status.data_ptr(), _stream()), "fa_fwd")
             if _SYNC_STATUS:
                 check_status(q.device)
         # autograd context (flash_triton.py:558-562); eq/ek are kept for the saved-tensor contract,
@@ -200,21 +228,24 @@ class FlashAttention(torch.autograd.Function):
             tq, tk, tv, to, tdo = _tensor(q), _tensor(k), _tensor(v), _tensor(o), _tensor(do)
             # delta = rowsum(o * do) (flash_triton.py:584-592)
             delta = torch.empty_like(L)
-            _lib.check(lib.fa_bwd_delta(ctypes.byref(prob), ctypes.byref(to), ctypes.byref(tdo), delta.data_ptr(),
-                                        stream), "fa_bwd_delta")
+            with _Timed("delta"):
+                _lib.check(lib.fa_bwd_delta(ctypes.byref(prob), ctypes.byref(to), ctypes.byref(tdo), delta.data_ptr(),
+                                            stream), "fa_bwd_delta")
             # dk, dv (flash_triton.py:594-614, group sum of :635-637 done inside the kernel)
             dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=q.device)
             dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=q.device)
             tdk, tdv = _tensor(dk), _tensor(dv)
-            _lib.check(lib.fa_bwd_dkdv(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
-                                       ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdk),
-                                       ctypes.byref(tdv), plan_ptr, status.data_ptr(), stream), "fa_bwd_dkdv")
+            with _Timed("dkdv"):
+                _lib.check(lib.fa_bwd_dkdv(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                           ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdk),
+                                           ctypes.byref(tdv), plan_ptr, status.data_ptr(), stream), "fa_bwd_dkdv")
             # dq (flash_triton.py:616-634); every row is written by the kernel
             dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
             tdq = _tensor(dq)
-            _lib.check(lib.fa_bwd_dq(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
-                                     ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdq), plan_ptr,
-                                     status.data_ptr(), stream), "fa_bwd_dq")
+            with _Timed("dq"):
+                _lib.check(lib.fa_bwd_dq(ctypes.byref(prob), ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                         ctypes.byref(tdo), L.data_ptr(), delta.data_ptr(), ctypes.byref(tdq), plan_ptr,
+                                         status.data_ptr(), stream), "fa_bwd_dq")
             if _SYNC_STATUS:
                 check_status(q.device)
         return dq, dk, dv, None, None, None, None, None
