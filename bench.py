@@ -117,9 +117,9 @@ def dist_env():
 # ------------------------------------------------------------------------------------------
 # CPU leg: the reference's masked-attention computation on the host cores, bounded sample
 # ------------------------------------------------------------------------------------------
-def cpu_sample(name, steps=1, warmup=0, rows=2048):
-    """Times forward+backward of the LAST `rows` queries of one head against all keys they can
-    see (the longest rows of the causal workload), fp32, all host threads."""
+def cpu_sample(name, steps=1, warmup=0, rows=None):
+    """Times forward+backward of ONE (batch, head) of the workload (all its query rows unless `rows`
+    limits it to the last ones), fp32, all host threads: 1/(B*H) of a step."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import attention_oracle as orc
     cfg = workloads.CONFIGS[name]
@@ -127,7 +127,7 @@ def cpu_sample(name, steps=1, warmup=0, rows=2048):
     rng = np.random.default_rng(workloads.SEEDS[name])
     eq_np, ek_np = workloads.doc_ids(name, rng, B=1)
     g = torch.Generator().manual_seed(workloads.SEEDS[name])
-    rows = min(rows, M)
+    rows = M if rows is None else min(rows, M)
     q = torch.randn(rows, D, generator=g) * cfg["std"]
     k = torch.randn(N, D, generator=g) * cfg["std"]
     v = torch.randn(N, D, generator=g) * cfg["std"]
@@ -147,7 +147,7 @@ def cpu_sample(name, steps=1, warmup=0, rows=2048):
     sec = float(np.mean(times))
     flops = 14.0 * D * nnz
     return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{name}: last {rows} query rows of one head x all {N} keys, fwd+bwd, fp32 torch on CPU, "
+            "sample": f"{name}: one of the {cfg['B'] * cfg['H']} (batch, head) pairs, {rows} query rows x {N} keys, fwd+bwd, fp32 torch on CPU, "
                       f"{sec * 1e3:.0f} ms per pass, nnz={nnz}",
             "ms_per_step": sec * 1e3}
 
@@ -190,10 +190,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
-    cfg = workloads.CONFIGS[name]
+    cfg = dict(workloads.CONFIGS[name])
+    if args.batch:
+        cfg["B"] = args.batch
+    if args.heads:
+        cfg["H"] = cfg["Hk"] = args.heads
     dim, qs, _ = shard.shard_slices(cfg["B"], cfg["H"], cfg["Hk"], world, rank)
     n_local = len(range(*qs.indices(cfg["H"] if dim == 1 else cfg["B"])))
-    kw = {"H": n_local} if dim == 1 else {"B": n_local}
+    kw = {"H": n_local, "B": cfg["B"]} if dim == 1 else {"B": n_local, "H": cfg["H"]}
     w = workloads.make_inputs(name, device=dev, **kw)          # this rank's shard, same ids on every rank
     per_b = nnz_per_head(w)
     # equal shards with the same ids on every rank
@@ -348,6 +352,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=list(workloads.CONFIGS))
     ap.add_argument("--forward-only", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="override the batch size (small profiling cases)")
+    ap.add_argument("--heads", type=int, default=None, help="override the head count (small profiling cases)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
