@@ -41,7 +41,8 @@ enum fa_error {
     FA_ERR_TENSORMAP = 4,    /* the driver refused to encode a tensor map */
     FA_ERR_LAUNCH = 5,       /* kernel launch failed (cudaGetLastError) */
     FA_ERR_PLAN_SIZE = 6,    /* plan buffer too small / missing for FA_MODE1_DOC */
-    FA_ERR_NO_DRIVER = 7     /* cuTensorMapEncodeTiled could not be resolved */
+    FA_ERR_NO_DRIVER = 7,    /* cuTensorMapEncodeTiled could not be resolved */
+    FA_ERR_SCRATCH_LIMIT = 8 /* fa_fwd_static_plan: the plan does not fit in FA_STATIC_PLAN_BYTES */
 };
 
 typedef struct fa_problem {
@@ -106,6 +107,24 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
  * [B, id_heads, ceil(M/128), ceil(N/128)] bytes: bit0 visited, bit1 bound/causal check,
  * bit2 id check, bit3 query tail. Either pointer may be NULL. */
 int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream);
+
+/* Size of the plan array built into the library for fa_fwd_static_plan (1 MiB per GPU). It holds
+ * the plan of, e.g., one 32768-token sequence with head-broadcast ids (0.27 MB) or a batch of
+ * 12 such 4096-token sequences; fa_plan_bytes() tells the size for any problem. */
+#define FA_STATIC_PLAN_BYTES (1u << 20)
+
+/* Forward for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * launcher allocates with torch, flash_triton.py:539-540). Same result as fa_plan_build + fa_fwd,
+ * but the mask plan is built in a fixed FA_STATIC_PLAN_BYTES array inside the library instead of
+ * a caller-allocated buffer, and the call allocates nothing. q, k, v, o, lse, eq, ek, status are
+ * passed as for the other entry points (eq / ek may be NULL when mode == FA_MODE0_NOPE).
+ * Returns FA_ERR_SCRATCH_LIMIT when the plan would not fit. The array is shared by all calls on a
+ * GPU: it keeps the previous call's contents (every element read is overwritten first, nothing
+ * needs clearing) and calls that overlap on the same GPU race. The first call on a device looks
+ * up the array's address; make it before any stream capture on that device. */
+int fa_fwd_static_plan(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
+                       const fa_tensor* o, float* lse, const fa_ids* eq, const fa_ids* ek, int32_t* status,
+                       void* stream);
 
 /* Host-only helper, no GPU involved: the tile classification the kernels apply to tile
  * (qb, kb) given the id-code min/max of its query block and key block. Returns the tile_class

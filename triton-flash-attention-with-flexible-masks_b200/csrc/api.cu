@@ -122,6 +122,7 @@ const char* fa_error_string(int code) {
         case FA_ERR_LAUNCH: return "kernel launch failed";
         case FA_ERR_PLAN_SIZE: return "mask plan missing or too small";
         case FA_ERR_NO_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled not available";
+        case FA_ERR_SCRATCH_LIMIT: return "mask plan larger than the library's built-in FA_STATIC_PLAN_BYTES array";
         default: return "unknown error";
     }
 }
