@@ -9,10 +9,11 @@
 //   warps 0-7  two compute groups; thread r of group g owns key row r and query columns
 //              [64g, 64g+64) of every tile
 //   warp 8     TMA producer (K, V once; Q ring with the per-row LSE / delta / id codes; dO ring)
-//   warp 9     tcgen05.mma issuer, owns TMEM
+//   warps 9,10 tcgen05.mma issuers (warp 9 also owns the TMEM allocation)
 // TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [256+D,256+2D).
 #include "common.cuh"
 #include "params.cuh"
+#include "trace.cuh"
 
 namespace fa {
 
@@ -60,6 +61,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int kb = blockIdx.x;  // with a causal mask the first key blocks are the long ones
@@ -93,13 +95,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(BAR(B_KV), 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(BAR(B_QFULL + s), 1); mbar_init(BAR(B_DOFULL + s), 1);
-            mbar_init(BAR(B_QEMPTY + s), 1); mbar_init(BAR(B_DOEMPTY + s), 1);
+            mbar_init(BAR(B_QEMPTY + s), 2); mbar_init(BAR(B_DOEMPTY + s), 2);  // one commit per MMA issuer
         }
         mbar_init(BAR(B_SFULL), 1);
         mbar_init(BAR(B_DPFULL), 1);
         mbar_init(BAR(B_PFULL), 256);
         mbar_init(BAR(B_DSFULL), 256);
-        mbar_init(BAR(B_DONE), 1);
+        mbar_init(BAR(B_DONE), 2);
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
         misc[2] = 0;
         fence_mbar_init();
@@ -166,63 +168,94 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         tma_load_4d(sdO(st) + x * S::BOX, &tmdO, BAR(B_DOFULL + st), x * 64, qb * kBlk, h, b);
                 }
             }
-        } else if (warp == 9) {
-            // ------------------------------ MMA issuer ------------------------------
+        } else if (warp == 9 || warp == 10) {
+            // ------------------------------ MMA issuers ------------------------------
+            // Two issuing threads, so that neither the blocking tcgen05.mma issue nor the barrier
+            // round trips of one pair of GEMMs delay the other pair:
+            //   warp 9 : dV(it) += P^T dO, then S^T(it+1) = K Q^T  (S^T overwrites P^T: same thread, in order)
+            //   warp 10: dK(it) += dS^T Q, then dP^T(it+1) = V dO^T (dP^T overwrites dS^T: same thread)
+            // Each Q / dO stage is read by both threads, so its "empty" barrier takes two commits.
             if (lane == 0) {
+                const bool is_a = (warp == 9);
                 constexpr uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
                 constexpr uint32_t idesc_d = make_idesc(BF16, 128, D, false, true);
                 constexpr uint64_t desc_mn = desc_mn_major(S::BOX);
                 bool ok = mbar_wait(BAR(B_KV), 0, ab, ST_WAIT_TIMEOUT + 43);
-                auto issue_s = [&](int it) {  // S^T = K Q^T
-                    const int st = it % NST, use = it / NST;
-                    if (!mbar_wait(BAR(B_QFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 44)) return false;
-                    tc_fence_after();
+                auto q_ready = [&](int it) { return mbar_wait(BAR(B_QFULL + it % NST), (it / NST) & 1, ab, ST_WAIT_TIMEOUT + 44); };
+                auto do_ready = [&](int it) { return mbar_wait(BAR(B_DOFULL + it % NST), (it / NST) & 1, ab, ST_WAIT_TIMEOUT + 45); };
+                auto ss_mmas = [&](uint32_t d, uint32_t a_tile, uint32_t b_tile) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(tmem, smem_desc_at(kDescKMajor, sK + off), smem_desc_at(kDescKMajor, sQ(st) + off),
+                        umma_ss(d, smem_desc_at(kDescKMajor, a_tile + off), smem_desc_at(kDescKMajor, b_tile + off),
                                 idesc_s, kk > 0);
                     }
-                    umma_commit(BAR(B_SFULL));
-                    return true;
                 };
-                auto issue_dp = [&](int it) {  // dP^T = V dO^T
-                    const int st = it % NST, use = it / NST;
-                    if (!mbar_wait(BAR(B_DOFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 45)) return false;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(tmem + 128u, smem_desc_at(kDescKMajor, sV + off),
-                                smem_desc_at(kDescKMajor, sdO(st) + off), idesc_s, kk > 0);
-                    }
-                    umma_commit(BAR(B_DPFULL));
-                    return true;
-                };
-                auto issue_acc = [&](int it, uint32_t a_base, uint32_t d, uint32_t b_tile, int empty_bar) {
+                auto acc_mmas = [&](int it, uint32_t a_base, uint32_t d, uint32_t b_tile) {
 #pragma unroll
                     for (int kk = 0; kk < kBlk / 16; ++kk) {
                         const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
                         umma_ts(d, a_base + acol, smem_desc_at(desc_mn, b_tile + uint32_t(kk) * 2048u), idesc_d,
                                 (it > 0 || kk > 0) ? 1u : 0u);
                     }
-                    umma_commit(BAR(empty_bar));
                 };
-                if (ok) ok = issue_s(0);
-                if (ok) ok = issue_dp(0);
-                for (int it = 0; it < NIT && ok; ++it) {
-                    const int st = it % NST;
-                    ok = mbar_wait(BAR(B_PFULL), it & 1, ab, ST_WAIT_TIMEOUT + 46);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_acc(it, tmem, tmem + 256u, sdO(st), B_DOEMPTY + st);             // dV += P^T dO
-                    if (it + 1 < NIT) ok = issue_s(it + 1);
-                    if (!ok) break;
-                    ok = mbar_wait(BAR(B_DSFULL), it & 1, ab, ST_WAIT_TIMEOUT + 47);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_acc(it, tmem + 128u, tmem + 256u + uint32_t(D), sQ(st), B_QEMPTY + st);  // dK += dS^T Q
-                    if (it + 1 < NIT) ok = issue_dp(it + 1);
+                if (is_a) {
+                    if (ok) ok = q_ready(0);
+                    if (ok) {
+                        tc_fence_after();
+                        ss_mmas(tmem, sK, sQ(0));  // S^T(0)
+                        umma_commit(BAR(B_QEMPTY + 0));
+                        umma_commit(BAR(B_SFULL));
+                    }
+                    for (int it = 0; it < NIT && ok; ++it) {
+                        const int st = it % NST;
+                        const bool more = it + 1 < NIT;
+                        ok = do_ready(it);
+                        FA_TRACE_EV(2, 3);
+                        if (ok) ok = mbar_wait(BAR(B_PFULL), it & 1, ab, ST_WAIT_TIMEOUT + 46);
+                        if (!ok) break;
+                        tc_fence_after();
+                        FA_TRACE_EV(2, 4);
+                        acc_mmas(it, tmem, tmem + 256u, sdO(st));  // dV += P^T dO
+                        umma_commit(BAR(B_DOEMPTY + st));
+                        // Q(it+1) can only be loaded once dK(it-1) has released its stage, so it is
+                        // waited for here and not ahead of P(it)
+                        if (more) ok = q_ready(it + 1);
+                        if (ok && more) {
+                            tc_fence_after();
+                            ss_mmas(tmem, sK, sQ((it + 1) % NST));
+                            umma_commit(BAR(B_QEMPTY + (it + 1) % NST));
+                            umma_commit(BAR(B_SFULL));
+                        }
+                        FA_TRACE_EV(2, 2);
+                    }
+                } else {
+                    if (ok) ok = do_ready(0);
+                    if (ok) {
+                        tc_fence_after();
+                        ss_mmas(tmem + 128u, sV, sdO(0));  // dP^T(0)
+                        umma_commit(BAR(B_DOEMPTY + 0));
+                        umma_commit(BAR(B_DPFULL));
+                    }
+                    for (int it = 0; it < NIT && ok; ++it) {
+                        const int st = it % NST;
+                        const bool more = it + 1 < NIT;
+                        ok = q_ready(it);
+                        if (ok && more) ok = do_ready(it + 1);
+                        if (ok) ok = mbar_wait(BAR(B_DSFULL), it & 1, ab, ST_WAIT_TIMEOUT + 47);
+                        // S^T(it+1) gates the next P and must not share the tensor pipe with this
+                        // batch (the pipe serves both issuers in turn): let it finish first
+                        if (ok && more) ok = mbar_wait(BAR(B_SFULL), (it + 1) & 1, ab, ST_WAIT_TIMEOUT + 49);
+                        if (!ok) break;
+                        tc_fence_after();
+                        acc_mmas(it, tmem + 128u, tmem + 256u + uint32_t(D), sQ(st));  // dK += dS^T Q
+                        umma_commit(BAR(B_QEMPTY + st));
+                        if (more) {
+                            ss_mmas(tmem + 128u, sV, sdO((it + 1) % NST));
+                            umma_commit(BAR(B_DOEMPTY + (it + 1) % NST));
+                            umma_commit(BAR(B_DPFULL));
+                        }
+                    }
                 }
                 if (ok) umma_commit(BAR(B_DONE));
             }
@@ -252,23 +285,32 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float* vdelta = vlse + kBlk;
             const int* vqc = reinterpret_cast<const int*>(vlse + 2 * kBlk);
 
+            if (r == 0) FA_TRACE_EV(w, 10);
             ok = mbar_wait(BAR(B_QFULL + st), (it / NST) & 1, ab, ST_WAIT_TIMEOUT + 48);
             if (ok) ok = mbar_wait(BAR(B_SFULL), it & 1, ab, ST_WAIT_TIMEOUT + 49);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (r == 0) FA_TRACE_EV(w, 11);
             uint32_t sr[64];
             tmem_ld32(tS, sr);
             tmem_ld32(tS + 32u, sr + 32);
             tc_wait_ld();
+            if (r == 0) FA_TRACE_EV(w, 12);
             float* pr = reinterpret_cast<float*>(sr);
+            {
+                const uint64_t c2 = pack_f2(c, c);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                const float4 l4 = *reinterpret_cast<const float4*>(vlse + 4 * q);
-                pr[4 * q + 0] = fast_exp2(fmaf(pr[4 * q + 0], c, -l4.x));
-                pr[4 * q + 1] = fast_exp2(fmaf(pr[4 * q + 1], c, -l4.y));
-                pr[4 * q + 2] = fast_exp2(fmaf(pr[4 * q + 2], c, -l4.z));
-                pr[4 * q + 3] = fast_exp2(fmaf(pr[4 * q + 3], c, -l4.w));
+                for (int q = 0; q < 16; ++q) {
+                    const float4 l4 = *reinterpret_cast<const float4*>(vlse + 4 * q);
+                    float x0, x1, x2, x3;
+                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 0], pr[4 * q + 1]), c2, pack_f2(-l4.x, -l4.y)), x0, x1);
+                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 2], pr[4 * q + 3]), c2, pack_f2(-l4.z, -l4.w)), x2, x3);
+                    pr[4 * q + 0] = fast_exp2(x0);
+                    pr[4 * q + 1] = fast_exp2(x1);
+                    pr[4 * q + 2] = fast_exp2(x2);
+                    pr[4 * q + 3] = fast_exp2(x3);
+                }
             }
             if (fl & (TILE_BOUND | TILE_DOC | TILE_QTAIL)) {
                 int cmin = -0x40000000, cmax = 64;  // keep iff cmin <= column < cmax
@@ -296,29 +338,35 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(BAR(B_PFULL));
+            if (r == 0) FA_TRACE_EV(w, 15);
 
             ok = mbar_wait(BAR(B_DPFULL), it & 1, ab, ST_WAIT_TIMEOUT + 50);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (r == 0) FA_TRACE_EV(w, 16);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t dp[32];
                 tmem_ld32(tdP + uint32_t(q) * 32u, dp);
                 tc_wait_ld();
+                // masked entries have P == 0 exactly and dP - delta is finite, so dS is 0 there
 #pragma unroll
                 for (int x = 0; x < 16; ++x) {
                     const float2 dl = *reinterpret_cast<const float2*>(vdelta + 32 * q + 2 * x);
-                    const float p0 = pr[32 * q + 2 * x], p1 = pr[32 * q + 2 * x + 1];
-                    const float d0 = p0 * (__uint_as_float(dp[2 * x]) - dl.x);
-                    const float d1 = p1 * (__uint_as_float(dp[2 * x + 1]) - dl.y);
-                    pk[16 * q + x] = pack2<BF16>(p0 == 0.f ? 0.f : d0, p1 == 0.f ? 0.f : d1);
+                    float d0, d1;
+                    unpack_f2(mul_f2(pack_f2(pr[32 * q + 2 * x], pr[32 * q + 2 * x + 1]),
+                                     add_f2(pack_f2(__uint_as_float(dp[2 * x]), __uint_as_float(dp[2 * x + 1])),
+                                            pack_f2(-dl.x, -dl.y))),
+                              d0, d1);
+                    pk[16 * q + x] = pack2<BF16>(d0, d1);
                 }
             }
             tmem_st32(tdP, pk);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(BAR(B_DSFULL));
+            if (r == 0) FA_TRACE_EV(w, 17);
         }
 
         // ------------------------------ epilogue ------------------------------
@@ -375,6 +423,8 @@ static cudaError_t launch_dkdv_t(const CUtensorMap& tq, const CUtensorMap& tk, c
     kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, p);
     return cudaGetLastError();
 }
+
+FA_TRACE_DUMP_FN(fa_trace_dump_dkdv)
 
 cudaError_t launch_bwd_dkdv(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const CUtensorMap& tdo, const DkdvParams& p, int B, cudaStream_t stream) {

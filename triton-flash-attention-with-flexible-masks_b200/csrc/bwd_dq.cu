@@ -6,11 +6,12 @@
 //   warps 0-7  two compute groups; thread r of group g owns query row r and key columns
 //              [64g, 64g+64) of every tile
 //   warp 8     TMA producer (Q and dO once, K ring, V ring)
-//   warp 9     tcgen05.mma issuer, owns TMEM
+//   warps 9,10 tcgen05.mma issuers (warp 9 also owns the TMEM allocation)
 // TMEM columns: S0 [0,128) S1 [128,256) dP [256,384) dQ [384,384+D). dS (input dtype) is
 // written over the first half of each group's own S columns and fed to the dQ MMA from TMEM.
 #include "common.cuh"
 #include "params.cuh"
+#include "trace.cuh"
 
 namespace fa {
 
@@ -42,6 +43,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int qb = mk.L.nQ - 1 - int(blockIdx.x);
@@ -129,65 +131,77 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     }
                 }
             }
-        } else if (warp == 9) {
-            // ------------------------------ MMA issuer ------------------------------
+        } else if (warp == 9 || warp == 10) {
+            // ------------------------------ MMA issuers ------------------------------
+            // Two issuing threads, so that the blocking tcgen05.mma issue and barrier round trips of
+            // one stream do not delay the other:
+            //   warp 9 : S(0), S(1); then per tile dQ(t) += dS K(t) followed by S(t+2) (which
+            //            overwrites dS(t): same thread, in order)
+            //   warp 10: dP(t+1) = dO V(t+1)^T as soon as dS(t) has been written (dP columns free)
             if (lane == 0) {
                 constexpr uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
                 constexpr uint32_t idesc_dq = make_idesc(BF16, 128, D, false, true);
                 constexpr uint64_t desc_mn = desc_mn_major(S::BOX);
                 bool ok = mbar_wait(BAR(B_QDO), 0, ab, ST_WAIT_TIMEOUT + 23);
-                auto issue_s = [&](int t) {
-                    const int st = t % NSK, use = t / NSK;
-                    if (!mbar_wait(BAR(B_KFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 24)) return false;
-                    tc_fence_after();
-                    const uint32_t d = tmem + uint32_t(t & 1) * 128u;
+                auto k_ready = [&](int t) { return mbar_wait(BAR(B_KFULL + t % NSK), (t / NSK) & 1, ab, ST_WAIT_TIMEOUT + 24); };
+                auto v_ready = [&](int t) { return mbar_wait(BAR(B_VFULL + t % NSV), (t / NSV) & 1, ab, ST_WAIT_TIMEOUT + 25); };
+                auto ss_mmas = [&](uint32_t d, uint32_t a_tile, uint32_t b_tile) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(d, smem_desc_at(kDescKMajor, sQ + off), smem_desc_at(kDescKMajor, sK(st) + off),
+                        umma_ss(d, smem_desc_at(kDescKMajor, a_tile + off), smem_desc_at(kDescKMajor, b_tile + off),
                                 idesc_s, kk > 0);
                     }
-                    umma_commit(BAR(B_SFULL + (t & 1)));
-                    return true;
                 };
-                auto issue_dp = [&](int t) {
-                    const int st = t % NSV, use = t / NSV;
-                    if (!mbar_wait(BAR(B_VFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 25)) return false;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(tmem + 256u, smem_desc_at(kDescKMajor, sdO + off),
-                                smem_desc_at(kDescKMajor, sV(st) + off), idesc_s, kk > 0);
+                if (warp == 9) {
+                    for (int t = 0; t < 2 && t < T && ok; ++t) {
+                        ok = k_ready(t);
+                        if (ok) {
+                            tc_fence_after();
+                            ss_mmas(tmem + uint32_t(t) * 128u, sQ, sK(t % NSK));
+                            umma_commit(BAR(B_SFULL + t));
+                        }
                     }
-                    umma_commit(BAR(B_VEMPTY + st));
-                    umma_commit(BAR(B_DPFULL));
-                    return true;
-                };
-                auto issue_dq = [&](int t) {
-                    const int st = t % NSK;
-                    const uint32_t a = tmem + uint32_t(t & 1) * 128u;
+                    for (int t = 0; t < T && ok; ++t) {
+                        const int st = t % NSK;
+                        FA_TRACE_EV(2, 3);
+                        ok = mbar_wait(BAR(B_DSFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 26);
+                        if (!ok) break;
+                        tc_fence_after();
+                        FA_TRACE_EV(2, 4);
+                        const uint32_t a = tmem + uint32_t(t & 1) * 128u;
 #pragma unroll
-                    for (int kk = 0; kk < kBlk / 16; ++kk) {
-                        const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
-                        umma_ts(tmem + 384u, a + acol, smem_desc_at(desc_mn, sK(st) + uint32_t(kk) * 2048u), idesc_dq,
-                                (t > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < kBlk / 16; ++kk) {
+                            const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
+                            umma_ts(tmem + 384u, a + acol, smem_desc_at(desc_mn, sK(st) + uint32_t(kk) * 2048u), idesc_dq,
+                                    (t > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        umma_commit(BAR(B_KEMPTY + st));
+                        // K(t+2) reuses the stage that dQ(t-1) releases, so it is waited for only now
+                        if (t + 2 < T) {
+                            ok = k_ready(t + 2);
+                            if (ok) {
+                                tc_fence_after();
+                                ss_mmas(a, sQ, sK((t + 2) % NSK));
+                                umma_commit(BAR(B_SFULL + (t & 1)));
+                            }
+                        }
+                        FA_TRACE_EV(2, 5);
                     }
-                    umma_commit(BAR(B_KEMPTY + st));
-                };
-                if (ok) ok = issue_s(0);
-                if (ok) ok = issue_dp(0);
-                if (ok && T > 1) ok = issue_s(1);
-                for (int t = 0; t < T && ok; ++t) {
-                    ok = mbar_wait(BAR(B_DSFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 26);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (t + 1 < T) ok = issue_dp(t + 1);  // the dP columns are free once dS(t) is written
-                    if (!ok) break;
-                    issue_dq(t);
-                    if (t + 2 < T) ok = issue_s(t + 2);
+                    if (ok) umma_commit(BAR(B_DONE));
+                } else {
+                    for (int t = 0; t < T && ok; ++t) {
+                        const int st = t % NSV;
+                        ok = v_ready(t);
+                        // dP(t) may overwrite the dP columns once every thread has read dP(t-1)
+                        if (ok && t > 0) ok = mbar_wait(BAR(B_DSFULL + ((t - 1) & 1)), ((t - 1) >> 1) & 1, ab, ST_WAIT_TIMEOUT + 26);
+                        if (!ok) break;
+                        tc_fence_after();
+                        ss_mmas(tmem + 256u, sdO, sV(st));
+                        umma_commit(BAR(B_VEMPTY + st));
+                        umma_commit(BAR(B_DPFULL));
+                    }
                 }
-                if (ok) umma_commit(BAR(B_DONE));
             }
         }
         __syncwarp();
@@ -212,6 +226,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             const uint32_t fl = entry >> 10;
             const int k0 = (lo + int(entry & 1023u)) * kBlk + cbase;  // first key column of this thread
             const uint32_t tS = tmem + lane_base + uint32_t(t & 1) * 128u + uint32_t(cbase);
+            if (r == 0) FA_TRACE_EV(w, 10);
             ok = mbar_wait(BAR(B_SFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 27);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -221,8 +236,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             tmem_ld32(tS + 32u, sr + 32);
             tc_wait_ld();
             float* pr = reinterpret_cast<float*>(sr);
+            if (r == 0) FA_TRACE_EV(w, 12);
+            {
+                const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(-lse, -lse);
 #pragma unroll
-            for (int j = 0; j < 64; ++j) pr[j] = fast_exp2(fmaf(pr[j], c, -lse));
+                for (int j = 0; j < 32; ++j) {
+                    float x0, x1;
+                    unpack_f2(fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2), x0, x1);
+                    pr[2 * j] = fast_exp2(x0);
+                    pr[2 * j + 1] = fast_exp2(x1);
+                }
+            }
             if (fl & (TILE_BOUND | TILE_DOC)) {
                 int lim = 63;
                 if (fl & TILE_BOUND) {
@@ -245,29 +269,35 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     for (int j = 0; j < 64; ++j) pr[j] = (j <= lim) ? pr[j] : 0.f;
                 }
             }
+            if (r == 0) FA_TRACE_EV(w, 13);
             ok = mbar_wait(BAR(B_DPFULL), t & 1, ab, ST_WAIT_TIMEOUT + 28);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (r == 0) FA_TRACE_EV(w, 16);
             uint32_t pk[32];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t dp[32];
                 tmem_ld32(tmem + lane_base + 256u + uint32_t(cbase) + uint32_t(q) * 32u, dp);
                 tc_wait_ld();
+                // masked entries have P == 0 exactly and dP - delta is finite, so dS is 0 there
+                // (flash_triton.py:400-414)
+                const uint64_t nd2 = pack_f2(-delta, -delta);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    // masked entries have P == 0 exactly, so dS is 0 there (flash_triton.py:400-414)
-                    const float d0 = pr[32 * q + 2 * j] * (__uint_as_float(dp[2 * j]) - delta);
-                    const float d1 = pr[32 * q + 2 * j + 1] * (__uint_as_float(dp[2 * j + 1]) - delta);
-                    pk[16 * q + j] = pack2<BF16>(pr[32 * q + 2 * j] == 0.f ? 0.f : d0,
-                                                 pr[32 * q + 2 * j + 1] == 0.f ? 0.f : d1);
+                    float d0, d1;
+                    unpack_f2(mul_f2(pack_f2(pr[32 * q + 2 * j], pr[32 * q + 2 * j + 1]),
+                                     add_f2(pack_f2(__uint_as_float(dp[2 * j]), __uint_as_float(dp[2 * j + 1])), nd2)),
+                              d0, d1);
+                    pk[16 * q + j] = pack2<BF16>(d0, d1);
                 }
             }
             tmem_st32(tS, pk);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(BAR(B_DSFULL + (t & 1)));
+            if (r == 0) FA_TRACE_EV(w, 17);
         }
 
         // ------------------------------ epilogue ------------------------------
@@ -319,6 +349,8 @@ static cudaError_t launch_dq_t(const CUtensorMap& tq, const CUtensorMap& tk, con
     kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, p);
     return cudaGetLastError();
 }
+
+FA_TRACE_DUMP_FN(fa_trace_dump_dq)
 
 cudaError_t launch_bwd_dq(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const CUtensorMap& tdo, const DqParams& p, int B, cudaStream_t stream) {

@@ -7,18 +7,22 @@
 // One CTA = one block of 128 queries of one (batch, head). 12 warps:
 //   warps 0-3  softmax group 0, warps 4-7 softmax group 1 (thread r of a group owns row r)
 //   warp 8     TMA producer (Q once, then K and V rings)
-//   warp 9     tcgen05.mma issuer, owns the TMEM allocation
-//   warps 10-11 idle; they only complete the third warpgroup so that registers can be moved
+//   warps 9,10 tcgen05.mma issuers, one per softmax group; warp 9 owns the TMEM allocation
+//   warp 11    idle; it only completes the third warpgroup so that registers can be moved
 //              from it to the softmax groups (setmaxnreg works on whole warpgroups)
 // Visited key tiles alternate between the two groups: tile t uses score buffer S[t&1] and
 // accumulates into O[t&1] with its own running max / sum, so the tensor pipe computes
 // S(t+1) while group t&1 is busy with the softmax of tile t. The two partial results are
 // merged in the epilogue.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D, 256+2D).
 // P (input dtype, two values per column) overwrites the first 64 columns of its S buffer.
+#include <type_traits>
 #include "common.cuh"
 #include "params.cuh"
+#include "trace.cuh"
 
 namespace fa {
+
+constexpr int kPolyOf4 = 1;  // of every 4 pairs of scores, how many take the FMA-pipe exp2
 
 template <int D>
 struct FwdSmem {
@@ -32,8 +36,8 @@ struct FwdSmem {
     static constexpr int off_list = off_v + NS * TILE;  // uint16 [kListCap]
     static constexpr int off_bar = off_list + kListCap * 2;
     // barriers (8 bytes each): q_full, k_full[NS], v_full[NS], k_empty[NS], v_empty[NS],
-    // s_full[2], p_full[2], pv_done[2]
-    static constexpr int n_bar = 1 + 4 * NS + 6;
+    // s_full[2], p_half0[2], p_half1[2], pv_done[2], turn[2]
+    static constexpr int n_bar = 1 + 4 * NS + 10;
     static constexpr int off_misc = off_bar + n_bar * 8;  // tmem slot, abort flag, tile count
     static constexpr int total = off_misc + 16;
 };
@@ -47,6 +51,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int nQ = mk.L.nQ;
@@ -60,7 +65,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const uint32_t bar0 = sbase + S::off_bar;
     auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
     const int B_QFULL = 0, B_KFULL = 1, B_VFULL = 1 + NS, B_KEMPTY = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
-              B_SFULL = 1 + 4 * NS, B_PFULL = B_SFULL + 2, B_PVDONE = B_SFULL + 4;
+              B_SFULL = 1 + 4 * NS, B_PHALF0 = B_SFULL + 2, B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8;
     Abort ab{misc + 1, p.status};
 
     int lo, hi;
@@ -78,8 +83,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         for (int w = 0; w < 2; ++w) {
             mbar_init(BAR(B_SFULL + w), 1);
-            mbar_init(BAR(B_PFULL + w), 128);
+            mbar_init(BAR(B_PHALF0 + w), 128);
+            mbar_init(BAR(B_PHALF1 + w), 128);
             mbar_init(BAR(B_PVDONE + w), 1);
+            mbar_init(BAR(B_TURN + w), 128);
         }
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
         misc[2] = 0;
@@ -109,7 +116,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
 
     if (warp >= 8) {
-        setmaxnreg_dec<56>();
+        setmaxnreg_dec<72>();
         if (aborted || T == 0) {
             // nothing to load or multiply
         } else if (warp == 8) {
@@ -145,56 +152,72 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     }
                 }
             }
-        } else if (warp == 9) {
-            // ------------------------------ MMA issuer ------------------------------
+        } else if (warp == 9 || warp == 10) {
+            // ------------------------------ MMA issuers ------------------------------
+            // One issuing thread per softmax group: warp 9 owns the even visited tiles (S0 / O0),
+            // warp 10 the odd ones (S1 / O1). The two chains touch disjoint TMEM and only share the
+            // K / V rings, so neither thread ever waits on the other group's softmax. Within a
+            // chain the MMAs of P*V(t) and S(t+2) are issued back to back (the tensor pipe accepts
+            // only a few MMAs ahead and needs ~200 clocks to refill once drained): what S(t+2)
+            // needs from TMA is waited for before P(t) is.
             if (lane == 0) {
+                const int w = warp - 9;
                 constexpr uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
                 constexpr uint32_t idesc_pv = make_idesc(BF16, 128, D, false, true);
                 constexpr uint64_t desc_v = desc_mn_major(S::BOX);
+                const uint32_t tS = tmem + uint32_t(w) * 128u;
+                const uint32_t tO = tmem + 256u + uint32_t(w) * uint32_t(D);
                 bool ok = mbar_wait(BAR(B_QFULL), 0, ab, ST_WAIT_TIMEOUT + 3);
-                auto issue_s = [&](int t) {
-                    const int st = t % NS, use = t / NS;
-                    if (!mbar_wait(BAR(B_KFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 4)) return false;
-                    tc_fence_after();
-                    const uint32_t d = tmem + uint32_t(t & 1) * 128u;
+                auto s_mmas = [&](int t) {
+                    const int st = t % NS;
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(d, smem_desc_at(kDescKMajor, sQ + off), smem_desc_at(kDescKMajor, sK(st) + off),
+                        umma_ss(tS, smem_desc_at(kDescKMajor, sQ + off), smem_desc_at(kDescKMajor, sK(st) + off),
                                 idesc_s, kk > 0);
                     }
                     umma_commit(BAR(B_KEMPTY + st));
-                    umma_commit(BAR(B_SFULL + (t & 1)));
-                    return true;
+                    umma_commit(BAR(B_SFULL + w));
+                    if (w == 0) FA_TRACE_EV(2, 2);
                 };
-                auto issue_pv = [&](int t) {
-                    const int st = t % NS, use = t / NS;
-                    if (!mbar_wait(BAR(B_VFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 5)) return false;
-                    if (!mbar_wait(BAR(B_PFULL + (t & 1)), (t >> 1) & 1, ab, ST_WAIT_TIMEOUT + 6)) return false;
+                auto k_ready = [&](int t) {
+                    return mbar_wait(BAR(B_KFULL + (t % NS)), (t / NS) & 1, ab, ST_WAIT_TIMEOUT + 4);
+                };
+                if (ok && w < T) {
+                    ok = k_ready(w);
+                    if (ok) { tc_fence_after(); s_mmas(w); }
+                }
+                int n_my = 0;
+                for (int tp = w; tp < T && ok; tp += 2, ++n_my) {
+                    const int st = tp % NS, use = tp / NS;
+                    const bool more = tp + 2 < T;
+                    ok = mbar_wait(BAR(B_VFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 5);
+                    if (ok && more) ok = k_ready(tp + 2);
+                    if (w == 0) FA_TRACE_EV(2, 3);
+                    if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 6);
+                    if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem + 256u + uint32_t(t & 1) * uint32_t(D);
-                    const uint32_t a = tmem + uint32_t(t & 1) * 128u;
+                    if (w == 0) FA_TRACE_EV(2, 4);
 #pragma unroll
-                    for (int kk = 0; kk < kBlk / 16; ++kk) {
-                        umma_ts(d, a + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u),
-                                idesc_pv, (t >= 2 || kk > 0) ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv,
+                                (n_my > 0 || kk > 0) ? 1u : 0u);
+                    ok = mbar_wait(BAR(B_PHALF1 + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 6);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 4; kk < 8; ++kk)
+                        umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv, 1u);
                     umma_commit(BAR(B_VEMPTY + st));
-                    umma_commit(BAR(B_PVDONE + (t & 1)));
-                    return true;
-                };
-                int ts = 0;
-                if (ok && ts < T) ok = issue_s(ts++);
-                if (ok && ts < T) ok = issue_s(ts++);
-                for (int tp = 0; tp < T && ok; ++tp) {
-                    ok = issue_pv(tp);
-                    if (ok && ts < T) ok = issue_s(ts++);
+                    umma_commit(BAR(B_PVDONE + w));
+                    if (w == 0) FA_TRACE_EV(2, 5);
+                    if (more) s_mmas(tp + 2);
                 }
             }
         }
         __syncwarp();
     } else {
-        setmaxnreg_inc<224>();
+        setmaxnreg_inc<216>();
         // ------------------------------ softmax groups ------------------------------
         const int w = warp >> 2;           // group
         const int r = tid & 127;           // row inside the block
@@ -209,19 +232,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t tS = tmem + lane_base + uint32_t(w) * 128u;
         const uint32_t tO = tmem + lane_base + 256u + uint32_t(w) * uint32_t(D);
 
+        const int n_other = (w == 0) ? T / 2 : (T + 1) / 2;  // tiles of the other group
+        if (w == 1 && T > 0 && ok) mbar_arrive(BAR(B_TURN + 0));  // group 0 takes the first turn
         for (int t = w; t < T && ok; t += 2, ++n_my) {
             const uint32_t entry = list[t];
             const uint32_t fl = entry >> 10;
             const int k0 = (lo + int(entry & 1023u)) * kBlk;
+            if (r == 0) FA_TRACE_EV(w, 10);
             ok = mbar_wait(BAR(B_SFULL + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 7);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (r == 0) FA_TRACE_EV(w, 11);
             uint32_t sr[128];
 #pragma unroll
             for (int q = 0; q < 4; ++q) tmem_ld32(tS + uint32_t(q) * 32u, sr + q * 32);
             tc_wait_ld();
             float* s = reinterpret_cast<float*>(sr);
+            if (r == 0) FA_TRACE_EV(w, 12);
 
             if (fl & (TILE_BOUND | TILE_DOC)) {
                 int lim = kBlk - 1;
@@ -245,9 +273,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     for (int j = 0; j < 128; ++j) s[j] = (j <= lim) ? s[j] : -INFINITY;
                 }
             }
-            float mx = s[0];
+            if (r == 0) FA_TRACE_EV(w, 18);
+            float mxa[8];
 #pragma unroll
-            for (int j = 1; j < 128; ++j) mx = fmaxf(mx, s[j]);
+            for (int a = 0; a < 8; ++a) mxa[a] = max3(s[a], s[8 + a], s[16 + a]);
+#pragma unroll
+            for (int j = 24; j < 120; j += 16) {
+#pragma unroll
+                for (int a = 0; a < 8; ++a) mxa[a] = max3(mxa[a], s[j + a], s[j + 8 + a]);
+            }
+#pragma unroll
+            for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], s[120 + a]);
+            const float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), max3(max3(mxa[3], mxa[4], mxa[5]), mxa[6], mxa[7]));
+            if (r == 0) FA_TRACE_EV(w, 19);
             float m_new = fmaxf(m_run, mx);
             // lazy rescale: keep the old reference point while the new maximum is within 2^8 of it
             const bool need = (m_new - m_run) * c > 8.0f;
@@ -272,25 +310,65 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     tc_wait_st();
                 }
             }
+            if (r == 0) FA_TRACE_EV(w, 13);
             m_run = m_new;
             const float mneg = (m_run == -INFINITY) ? 0.f : -m_run * c;
-            float lsum = 0.f;
+            // exp2(s*c - m*c) on packed pairs; P goes to TMEM in two halves so that the first four
+            // k-steps of P*V can start while the second half is still being exponentiated. MUFU
+            // (16 ex2 per clock and SM) is as scarce as the tensor pipe here, so on tiles without
+            // masked entries kPolyOf4 of every 4 pairs are evaluated on the FMA pipe instead.
+            const uint64_t c2 = pack_f2(c, c), mneg2 = pack_f2(mneg, mneg);
+            uint64_t lacc0 = pack_f2(0.f, 0.f), lacc1 = lacc0;
+            // The exp phase is taken in turns (barriers turn[0], turn[1]; group 0 first): left alone,
+            // the groups fall into lockstep, exponentiate together at half MUFU rate each and then
+            // queue their MMAs together, which halves the use of both pipes. In turns, one group
+            // exponentiates while the other group's P*V and next S run on the tensor pipe.
+            ok = mbar_wait(BAR(B_TURN + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 10);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
+            auto exp_half = [&](auto use_poly, int half) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t pk[16];
+                for (int q = 2 * half; q < 2 * half + 2; ++q) {
+                    uint32_t pk[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float p0 = fast_exp2(fmaf(s[32 * q + 2 * j], c, mneg));
-                    const float p1 = fast_exp2(fmaf(s[32 * q + 2 * j + 1], c, mneg));
-                    lsum += p0 + p1;
-                    pk[j] = pack2<BF16>(p0, p1);
+                    for (int j = 0; j < 16; ++j) {
+                        const uint64_t x2 = fma_f2(pack_f2(s[32 * q + 2 * j], s[32 * q + 2 * j + 1]), c2, mneg2);
+                        float p0, p1;
+                        if (decltype(use_poly)::value && (j & 3) < kPolyOf4) {
+                            exp2_poly2(x2, p0, p1);
+                        } else {
+                            float x0, x1;
+                            unpack_f2(x2, x0, x1);
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
+                        if (j & 1) lacc1 = add_f2(lacc1, pack_f2(p0, p1)); else lacc0 = add_f2(lacc0, pack_f2(p0, p1));
+                        pk[j] = pack2<BF16>(p0, p1);
+                    }
+                    tmem_st16(tS + uint32_t(q) * 16u, pk);
                 }
-                tmem_st16(tS + uint32_t(q) * 16u, pk);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(BAR((half ? B_PHALF1 : B_PHALF0) + w));
+                if (r == 0) FA_TRACE_EV(w, 14 + half);
+            };
+            if (poly_ok) {
+                exp_half(std::true_type{}, 0);
+                exp_half(std::true_type{}, 1);
+            } else {
+                exp_half(std::false_type{}, 0);
+                exp_half(std::false_type{}, 1);
             }
-            l_run += lsum;
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(BAR(B_PFULL + w));
+            // hand the turn over, unless the other group has no tile left to take it for
+            if (w == 0 ? (n_my < n_other) : (n_my + 1 < n_other)) mbar_arrive(BAR(B_TURN + (w ^ 1)));
+            {
+                float a0, a1, b0, b1;
+                unpack_f2(lacc0, a0, a1);
+                unpack_f2(lacc1, b0, b1);
+                l_run += (a0 + a1) + (b0 + b1);
+            }
+            if (r == 0) FA_TRACE_EV(w, 15);
         }
 
         // ------------------------------ epilogue ------------------------------
@@ -384,6 +462,8 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
     kern<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
+
+FA_TRACE_DUMP_FN(fa_trace_dump_fwd)
 
 cudaError_t launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                        const FwdParams& p, int B, cudaStream_t stream) {
