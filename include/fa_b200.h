@@ -105,7 +105,8 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
 /* Debug: materialise the kernels' decisions. keep is [B, id_heads, M, N] bytes (1 = unmasked),
  * produced by the same device predicate the attention kernels use; tile_class is
  * [B, id_heads, ceil(M/128), ceil(N/128)] bytes: bit0 visited, bit1 bound/causal check,
- * bit2 id check, bit3 query tail. Either pointer may be NULL. */
+ * bit2 id check, bit3 query tail, bit4 / bit5 key / query codes of the block are monotone.
+ * Either pointer may be NULL. */
 int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t* tile_class, void* stream);
 
 /* Size of the plan array built into the library for fa_fwd_static_plan (1 MiB per GPU). It holds

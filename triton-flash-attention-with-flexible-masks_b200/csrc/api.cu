@@ -9,8 +9,8 @@ namespace fa {
 cudaError_t launch_plan_build(const void*, const int64_t*, int, const void*, const int64_t*, int, int32_t*,
                               const PlanLayout&, int, int, int*, cudaStream_t);
 cudaError_t launch_debug_mask(const MaskArgs&, uint8_t*, uint8_t*, cudaStream_t);
-cudaError_t launch_fwd(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FwdParams&,
-                       int, cudaStream_t);
+cudaError_t launch_fwd(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                       const FwdParams&, int, cudaStream_t);
 cudaError_t launch_bwd_delta(const DeltaParams&, cudaStream_t);
 cudaError_t launch_bwd_dkdv(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
                             const CUtensorMap&, const DkdvParams&, int, cudaStream_t);
@@ -103,6 +103,21 @@ fa::OutTensor out_view(const fa_tensor* t) { return fa::OutTensor{t->ptr, t->str
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Number of SMs of the current device (persistent kernels launch one CTA per SM); cached per device.
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return -1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 }  // namespace
 
 extern "C" {
@@ -171,18 +186,21 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     if ((rc = check_tensor(o, p->B, p->H, p->M))) return rc;
     fa::FwdParams fp;
     if ((rc = make_mask(&fp.mask, p, plan))) return rc;
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, to;
     if ((rc = make_map(&tq, q, p->dtype, p->B, p->H, p->M, p->D))) return rc;
     if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
-    fp.o = out_view(o);
+    if ((rc = make_map(&to, o, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    const int sms = sm_count();
+    if (sms <= 0) return FA_ERR_LAUNCH;
     fp.lse = lse;
     fp.H = p->H;
+    fp.B = p->B;
     fp.G = p->H / p->Hk;
     fp.scale_log2 = p->sm_scale * kLog2e;
     fp.status = status;
     const cudaError_t e =
-        fa::launch_fwd(p->D, p->dtype == FA_BF16, tq, tk, tv, fp, p->B, static_cast<cudaStream_t>(stream));
+        fa::launch_fwd(p->D, p->dtype == FA_BF16, tq, tk, tv, to, fp, sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
 }
 

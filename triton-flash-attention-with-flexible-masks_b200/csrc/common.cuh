@@ -25,10 +25,12 @@ __host__ __device__ inline int64_t pad128(int64_t x) { return (x + 127) / 128 * 
 //   kmin, kmax [B, He, nK]   min / max key code per block of 128 keys
 //   kv_lo, kv_hi [B, He, nQ] range of key blocks with an unmasked entry, per query block
 //   q_lo, q_hi   [B, He, nK] range of query blocks with an unmasked entry, per key block
+//   qmono [B, He, nQ], kmono [B, He, nK]  1 if the codes of the block are monotone (non-decreasing or
+//                non-increasing), i.e. equal codes are adjacent: the usual packed-documents layout
 struct PlanLayout {
     int B, He, M, N, nQ, nK;
     int64_t Mpad, Npad;
-    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi;
+    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi, off_qmono, off_kmono;
     int64_t total;  // int32 elements
 
     __host__ __device__ PlanLayout() {}
@@ -48,6 +50,8 @@ struct PlanLayout {
         off_kvhi = o; o += pad128(bh * nQ);
         off_qlo = o;  o += pad128(bh * nK);
         off_qhi = o;  o += pad128(bh * nK);
+        off_qmono = o; o += pad128(bh * nQ);
+        off_kmono = o; o += pad128(bh * nK);
         total = o;
     }
 };
@@ -65,6 +69,8 @@ enum : uint32_t {
     TILE_BOUND = 2u,   // needs the per-entry j < N / causal check
     TILE_DOC = 4u,     // needs the per-entry id check
     TILE_QTAIL = 8u,   // holds rows >= M (matters to the backward kernels only)
+    TILE_KMONO = 16u,  // key codes of the block are monotone: a 32-key chunk is uniform iff its ends are equal
+    TILE_QMONO = 32u,  // same for the query codes of the block
 };
 
 // Classification of tile (qb, kb) from the block statistics. Conservative: a tile is skipped
@@ -99,7 +105,13 @@ __device__ __forceinline__ uint32_t classify_from_plan(const MaskArgs& a, int b,
         kmin = a.plan[a.L.off_kmin + bh * a.L.nK + kb];
         kmax = a.plan[a.L.off_kmax + bh * a.L.nK + kb];
     }
-    return classify_tile(qb, kb, a.M, a.N, a.gap, a.causal, a.mode, qmin, qmax, kmin, kmax);
+    uint32_t f = classify_tile(qb, kb, a.M, a.N, a.gap, a.causal, a.mode, qmin, qmax, kmin, kmax);
+    if (a.mode == 1 && (f & TILE_DOC)) {
+        const int64_t bh = int64_t(b) * a.He + he;
+        if (a.plan[a.L.off_kmono + bh * a.L.nK + kb]) f |= TILE_KMONO;
+        if (a.plan[a.L.off_qmono + bh * a.L.nQ + qb]) f |= TILE_QMONO;
+    }
+    return f;
 }
 
 // Key-block range [lo, hi) a query block has to walk.

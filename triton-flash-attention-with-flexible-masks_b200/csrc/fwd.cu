@@ -4,16 +4,22 @@
 // applied in fp32 to the fp32 scores instead of being folded into a rounded Q
 // (flash_triton.py:88), and tiles the mask plan proves empty are not visited at all.
 //
-// One CTA = one block of 128 queries of one (batch, head). 12 warps:
+// Persistent: one CTA per SM walks work items (one item = one block of 128 queries of one
+// (batch, head)); item j of CTA c is c + j * gridDim.x in an order that puts the query blocks of
+// all heads side by side, so that the CTAs of one round carry almost equal work. With document
+// masks most items hold only a few tiles, so everything around the tiles is overlapped with the
+// neighbouring items: a scheduler warp prepares the next item's tile list, the producer prefetches
+// its Q / K / V, and the output tile leaves through an asynchronous TMA store.
+//
+// 12 warps:
 //   warps 0-3  softmax group 0, warps 4-7 softmax group 1 (thread r of a group owns row r)
-//   warp 8     TMA producer (Q once, then K and V rings)
+//   warp 8     TMA producer (Q per item, K and V rings that run across items)
 //   warps 9,10 tcgen05.mma issuers, one per softmax group; warp 9 owns the TMEM allocation
-//   warp 11    idle; it only completes the third warpgroup so that registers can be moved
-//              from it to the softmax groups (setmaxnreg works on whole warpgroups)
-// Visited key tiles alternate between the two groups: tile t uses score buffer S[t&1] and
-// accumulates into O[t&1] with its own running max / sum, so the tensor pipe computes
-// S(t+1) while group t&1 is busy with the softmax of tile t. The two partial results are
-// merged in the epilogue.  TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D, 256+2D).
+//   warp 11    item scheduler: decodes the item, classifies its candidate tiles from the mask plan
+//              and compacts the visited ones into a list in shared memory (two item slots)
+// Visited key tiles of an item alternate between the two groups: tile t uses score buffer S[t&1]
+// and accumulates into O[t&1] with its own running max / sum; the two partial results are merged
+// in the item's epilogue. TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (input dtype, two values per column) overwrites the first 64 columns of its S buffer.
 #include <type_traits>
 #include "common.cuh"
@@ -23,29 +29,35 @@
 namespace fa {
 
 constexpr int kPolyOf4 = 1;  // of every 4 pairs of scores, how many take the FMA-pipe exp2
+constexpr int kTurnMinTiles = 8;  // items with fewer visited tiles do not serialise their exp phases
 
 template <int D>
 struct FwdSmem {
-    static constexpr int NS = (D == 128) ? 3 : 4;
+    static constexpr int NS = (D == 128) ? 2 : 4;  // depth of the K ring and of the V ring
     static constexpr int TILE = kBlk * D * 2;
     static constexpr int BOX = kBlk * 64 * 2;
     static constexpr int NBOX = D / 64;
-    static constexpr int off_q = 0;
-    static constexpr int off_k = TILE;
+    static constexpr int NKC = 8;  // depth of the key-code ring
+    static constexpr int off_q = 0;  // two Q tiles; a slot also stages its item's O tile for the TMA store
+    static constexpr int off_k = 2 * TILE;
     static constexpr int off_v = off_k + NS * TILE;
-    static constexpr int off_list = off_v + NS * TILE;  // uint16 [kListCap]
-    static constexpr int off_bar = off_list + kListCap * 2;
-    // barriers (8 bytes each): q_full, k_full[NS], v_full[NS], k_empty[NS], v_empty[NS],
-    // s_full[2], p_half0[2], p_half1[2], pv_done[2], turn[2]
-    static constexpr int n_bar = 1 + 4 * NS + 10;
-    static constexpr int off_misc = off_bar + n_bar * 8;  // tmem slot, abort flag, tile count
+    static constexpr int off_list = off_v + NS * TILE;         // uint16 [2][kListCap]
+    static constexpr int off_qc = off_list + 2 * kListCap * 2;  // int32  [2][128] query codes
+    static constexpr int off_kc = off_qc + 2 * kBlk * 4;        // int32  [NKC][128] key codes, loaded with K
+    static constexpr int off_ml = off_kc + NKC * kBlk * 4;      // float  [2][2 groups][m, l][128]
+    static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][4]: T, lo
+    static constexpr int off_bar = off_info + 32;
+    // item_full[2] item_empty[2] q_full[2] o_staged[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
+    // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] kc_full[NKC]
+    static constexpr int n_bar = 8 + 4 * NS + 12 + 8;
+    static constexpr int off_misc = off_bar + n_bar * 8;  // tmem slot, abort flag
     static constexpr int total = off_misc + 16;
 };
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-           const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FwdParams p) {
     using S = FwdSmem<D>;
     constexpr int NS = S::NS;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -55,104 +67,177 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
     const MaskArgs& mk = p.mask;
     const int nQ = mk.L.nQ;
-    const int qb = nQ - 1 - int(blockIdx.x);  // long causal rows first
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int hk = h / p.G;
-    const int he = (mk.He == 1) ? 0 : h;
+    const int HB = p.H * p.B;
+    const int n_items = nQ * HB;
 
-    uint16_t* list = reinterpret_cast<uint16_t*>(smem + S::off_list);
-    volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);  // [0] tmem, [1] abort, [2] T
+    volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);  // [0] tmem, [1] abort
+    volatile int* info = reinterpret_cast<volatile int*>(smem + S::off_info);
     const uint32_t bar0 = sbase + S::off_bar;
     auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
-    const int B_QFULL = 0, B_KFULL = 1, B_VFULL = 1 + NS, B_KEMPTY = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
-              B_SFULL = 1 + 4 * NS, B_PHALF0 = B_SFULL + 2, B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8;
+    constexpr int B_ITEMFULL = 0, B_ITEMEMPTY = 2, B_QFULL = 4, B_OSTAGED = 6, B_KFULL = 8, B_KEMPTY = 8 + NS,
+                  B_VFULL = 8 + 2 * NS, B_VEMPTY = 8 + 3 * NS, B_SFULL = 8 + 4 * NS, B_PHALF0 = B_SFULL + 2,
+                  B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_KCFULL = B_SFULL + 12;
     Abort ab{misc + 1, p.status};
 
-    int lo, hi;
-    kv_range(mk, b, he, qb, lo, hi);
-    int n = hi - lo;
-    if (n > kListCap) n = kListCap;  // the host refuses problems that could exceed the cap
-
     if (tid == 0) {
-        mbar_init(BAR(B_QFULL), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(BAR(B_ITEMFULL + s), 1);
+            mbar_init(BAR(B_ITEMEMPTY + s), 5);  // producer, two MMA issuers, one thread of each softmax group
+            mbar_init(BAR(B_QFULL + s), 1);
+            mbar_init(BAR(B_OSTAGED + s), 256);
+            mbar_init(BAR(B_SFULL + s), 1);
+            mbar_init(BAR(B_PHALF0 + s), 128);
+            mbar_init(BAR(B_PHALF1 + s), 128);
+            mbar_init(BAR(B_PVDONE + s), 1);
+            mbar_init(BAR(B_TURN + s), 128);
+            mbar_init(BAR(B_OFREE + s), 256);
+        }
+        for (int s = 0; s < S::NKC; ++s) mbar_init(BAR(B_KCFULL + s), 1);
         for (int s = 0; s < NS; ++s) {
             mbar_init(BAR(B_KFULL + s), 1);
-            mbar_init(BAR(B_VFULL + s), 1);
             mbar_init(BAR(B_KEMPTY + s), 1);
+            mbar_init(BAR(B_VFULL + s), 1);
             mbar_init(BAR(B_VEMPTY + s), 1);
         }
-        for (int w = 0; w < 2; ++w) {
-            mbar_init(BAR(B_SFULL + w), 1);
-            mbar_init(BAR(B_PHALF0 + w), 128);
-            mbar_init(BAR(B_PHALF1 + w), 128);
-            mbar_init(BAR(B_PVDONE + w), 1);
-            mbar_init(BAR(B_TURN + w), 128);
-        }
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
-        misc[2] = 0;
         fence_mbar_init();
     }
     if (warp == 9) {
         tmem_alloc(sbase + S::off_misc, 512);
         tmem_relinquish();
     }
-    // tile flags for [lo, lo+n)
-    for (int i = tid; i < n; i += kFwdThreads) list[i] = uint16_t(classify_from_plan(mk, b, he, qb, lo + i));
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // compaction to the visited list: entry = (index relative to lo) | flags << 10
-    if (warp == 0) {
-        const int T = compact_visit_list(list, n, lane);
-        if (lane == 0) misc[2] = T;
-    }
-    __syncthreads();
     const uint32_t tmem = uint32_t(misc[0]);
-    const int T = misc[2];
     const bool aborted = misc[1] != 0;
 
-    const uint32_t sQ = sbase + S::off_q;
+    auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
     auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };
     auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
+    auto list_of = [&](int s) { return reinterpret_cast<const uint16_t*>(smem + S::off_list) + s * kListCap; };
+    // item index -> (query block, head, batch): heads and batches vary fastest, long causal rows first
+    auto decode = [&](int j, int& qb, int& h, int& b) {
+        const int rank = j / HB, bh = j - rank * HB;
+        qb = nQ - 1 - rank;
+        b = bh / p.H;
+        h = bh - b * p.H;
+    };
 
     if (warp >= 8) {
         setmaxnreg_dec<72>();
-        if (aborted || T == 0) {
-            // nothing to load or multiply
+        if (aborted) {
+            // a previous kernel reported an error: do nothing
+        } else if (warp == 11) {
+            // ------------------------------ item scheduler ------------------------------
+            bool ok = true;
+            int k = 0;
+            for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+                const int s = k & 1, use = k >> 1;
+                if (use > 0) ok = mbar_wait(BAR(B_ITEMEMPTY + s), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 11);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                int qb, h, b;
+                decode(j, qb, h, b);
+                const int he = (mk.He == 1) ? 0 : h;
+                int lo, hi;
+                kv_range(mk, b, he, qb, lo, hi);
+                int n = hi - lo;
+                if (n > kListCap) n = kListCap;  // the host refuses problems that could exceed the cap
+                uint16_t* list = reinterpret_cast<uint16_t*>(smem + S::off_list) + s * kListCap;
+                int T = 0;
+                for (int base = 0; base < n; base += 32) {
+                    const int i = base + lane;
+                    const uint32_t f = (i < n) ? classify_from_plan(mk, b, he, qb, lo + i) : 0u;
+                    const uint32_t m = __ballot_sync(0xffffffffu, (f & TILE_VISIT) != 0);
+                    if (f & TILE_VISIT) list[T + __popc(m & ((1u << lane) - 1u))] = uint16_t(uint32_t(i) | (f << 10));
+                    T += __popc(m);
+                }
+                int4 qc4 = make_int4(0, 0, 0, 0);
+                if (mk.mode == 1)
+                    qc4 = *reinterpret_cast<const int4*>(mk.plan + mk.L.off_qc + (int64_t(b) * mk.He + he) * mk.L.Mpad +
+                                                         int64_t(qb) * kBlk + lane * 4);
+                reinterpret_cast<int4*>(smem + S::off_qc)[s * 32 + lane] = qc4;
+                if (lane == 0) {
+                    info[s * 4 + 0] = T;
+                    info[s * 4 + 1] = lo;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(B_ITEMFULL + s));
+            }
         } else if (warp == 8) {
             // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
                 tma_prefetch_desc(&tmQ);
                 tma_prefetch_desc(&tmK);
                 tma_prefetch_desc(&tmV);
-                mbar_expect_tx(BAR(B_QFULL), S::TILE);
-                for (int x = 0; x < S::NBOX; ++x)
-                    tma_load_4d(sQ + x * S::BOX, &tmQ, BAR(B_QFULL), x * 64, qb * kBlk, h, b);
                 bool ok = true;
-                // K runs one tile ahead of V
-                for (int t = 0; t <= T && ok; ++t) {
-                    if (t < T) {
-                        const int kb = lo + (list[t] & 1023);
-                        const int st = t % NS, use = t / NS;
-                        if (use > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 1);
-                        if (!ok) break;
-                        mbar_expect_tx(BAR(B_KFULL + st), S::TILE);
-                        for (int x = 0; x < S::NBOX; ++x)
-                            tma_load_4d(sK(st) + x * S::BOX, &tmK, BAR(B_KFULL + st), x * 64, kb * kBlk, hk, b);
+                int k = 0, G = 0;  // G: tiles of all earlier items (the K / V rings run across items)
+                // TMA store of the O tile the softmax groups staged in slot (kk & 1) for item kk
+                auto store_o = [&](int kk) {
+                    const int s = kk & 1;
+                    if (!mbar_wait(BAR(B_OSTAGED + s), (kk >> 1) & 1, ab, ST_WAIT_TIMEOUT + 13)) return false;
+                    int qb, h, b;
+                    decode(int(blockIdx.x) + kk * int(gridDim.x), qb, h, b);
+                    for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmO, sQ(s) + x * S::BOX, x * 64, qb * kBlk, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read();
+                    return true;
+                };
+                for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+                    const int s = k & 1, use = k >> 1;
+                    ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
+                    if (!ok) break;
+                    const int T = info[s * 4 + 0], lo = info[s * 4 + 1];
+                    const uint16_t* list = list_of(s);
+                    int qb, h, b;
+                    decode(j, qb, h, b);
+                    const int hk = h / p.G;
+                    const int he = (mk.He == 1) ? 0 : h;
+                    // the slot still holds the staged O tile of item k-2: send it off first
+                    if (use > 0) ok = store_o(k - 2);
+                    if (!ok) break;
+                    mbar_expect_tx(BAR(B_QFULL + s), S::TILE);
+                    for (int x = 0; x < S::NBOX; ++x)
+                        tma_load_4d(sQ(s) + x * S::BOX, &tmQ, BAR(B_QFULL + s), x * 64, qb * kBlk, h, b);
+                    for (int t = 0; t <= T && ok; ++t) {  // K runs one tile ahead of V
+                        if (t < T) {
+                            const int kb = lo + (list[t] & 1023);
+                            const int g = G + t, st = g % NS, ug = g / NS;
+                            if (ug > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 1);
+                            if (!ok) break;
+                            // The tile's key codes are fetched with K into a ring of NKC slots (own barriers). Slot g % NKC was
+                            // last read by the softmax of tile g - NKC, which is over: this thread has
+                            // already waited for the P*V of tile g - 2 - NS before issuing V(g - 2).
+                            mbar_expect_tx(BAR(B_KFULL + st), S::TILE);
+                            for (int x = 0; x < S::NBOX; ++x)
+                                tma_load_4d(sK(st) + x * S::BOX, &tmK, BAR(B_KFULL + st), x * 64, kb * kBlk, hk, b);
+                            if (mk.mode == 1) {
+                                mbar_expect_tx(BAR(B_KCFULL + g % S::NKC), kBlk * 4);
+                                bulk_load_1d(sbase + S::off_kc + (g % S::NKC) * (kBlk * 4),
+                                             mk.plan + mk.L.off_kc + (int64_t(b) * mk.He + he) * mk.L.Npad + int64_t(kb) * kBlk,
+                                             kBlk * 4, BAR(B_KCFULL + g % S::NKC));
+                            }
+                        }
+                        if (t >= 1) {
+                            const int kb = lo + (list[t - 1] & 1023);
+                            const int g = G + t - 1, st = g % NS, ug = g / NS;
+                            if (ug > 0) ok = mbar_wait(BAR(B_VEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 2);
+                            if (!ok) break;
+                            mbar_expect_tx(BAR(B_VFULL + st), S::TILE);
+                            for (int x = 0; x < S::NBOX; ++x)
+                                tma_load_4d(sV(st) + x * S::BOX, &tmV, BAR(B_VFULL + st), x * 64, kb * kBlk, hk, b);
+                        }
                     }
-                    if (t >= 1) {
-                        const int tv = t - 1;
-                        const int kb = lo + (list[tv] & 1023);
-                        const int st = tv % NS, use = tv / NS;
-                        if (use > 0) ok = mbar_wait(BAR(B_VEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 2);
-                        if (!ok) break;
-                        mbar_expect_tx(BAR(B_VFULL + st), S::TILE);
-                        for (int x = 0; x < S::NBOX; ++x)
-                            tma_load_4d(sV(st) + x * S::BOX, &tmV, BAR(B_VFULL + st), x * 64, kb * kBlk, hk, b);
-                    }
+                    G += T;
+                    if (ok) mbar_arrive(BAR(B_ITEMEMPTY + s));
                 }
+                // the last two items' tiles
+                if (ok && k >= 2) ok = store_o(k - 2);
+                if (ok && k >= 1) ok = store_o(k - 1);
+                tma_store_wait_all();
             }
-        } else if (warp == 9 || warp == 10) {
+        } else {
             // ------------------------------ MMA issuers ------------------------------
             // One issuing thread per softmax group: warp 9 owns the even visited tiles (S0 / O0),
             // warp 10 the odd ones (S1 / O1). The two chains touch disjoint TMEM and only share the
@@ -167,51 +252,63 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 constexpr uint64_t desc_v = desc_mn_major(S::BOX);
                 const uint32_t tS = tmem + uint32_t(w) * 128u;
                 const uint32_t tO = tmem + 256u + uint32_t(w) * uint32_t(D);
-                bool ok = mbar_wait(BAR(B_QFULL), 0, ab, ST_WAIT_TIMEOUT + 3);
-                auto s_mmas = [&](int t) {
-                    const int st = t % NS;
+                bool ok = true;
+                int k = 0, G = 0, cw = 0;  // cw: tiles this chain has finished (phases of its barriers)
+                for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+                    const int s = k & 1, use = k >> 1;
+                    ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
+                    if (!ok) break;
+                    const int T = info[s * 4 + 0];
+                    ok = mbar_wait(BAR(B_QFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 3);
+                    if (!ok) break;
+                    const uint32_t q_tile = sQ(s);
+                    auto k_ready = [&](int g) {
+                        return mbar_wait(BAR(B_KFULL + (g % NS)), (g / NS) & 1, ab, ST_WAIT_TIMEOUT + 4);
+                    };
+                    auto s_mmas = [&](int g) {
+                        const int st = g % NS;
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
-                        umma_ss(tS, smem_desc_at(kDescKMajor, sQ + off), smem_desc_at(kDescKMajor, sK(st) + off),
-                                idesc_s, kk > 0);
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
+                            umma_ss(tS, smem_desc_at(kDescKMajor, q_tile + off), smem_desc_at(kDescKMajor, sK(st) + off),
+                                    idesc_s, kk > 0);
+                        }
+                        umma_commit(BAR(B_KEMPTY + st));
+                        umma_commit(BAR(B_SFULL + w));
+                    };
+                    const int nmine = (T > w) ? (T - w + 1) / 2 : 0;
+                    if (nmine > 0) {
+                        ok = k_ready(G + w);
+                        if (!ok) break;
+                        tc_fence_after();
+                        s_mmas(G + w);
                     }
-                    umma_commit(BAR(B_KEMPTY + st));
-                    umma_commit(BAR(B_SFULL + w));
-                    if (w == 0) FA_TRACE_EV(2, 2);
-                };
-                auto k_ready = [&](int t) {
-                    return mbar_wait(BAR(B_KFULL + (t % NS)), (t / NS) & 1, ab, ST_WAIT_TIMEOUT + 4);
-                };
-                if (ok && w < T) {
-                    ok = k_ready(w);
-                    if (ok) { tc_fence_after(); s_mmas(w); }
-                }
-                int n_my = 0;
-                for (int tp = w; tp < T && ok; tp += 2, ++n_my) {
-                    const int st = tp % NS, use = tp / NS;
-                    const bool more = tp + 2 < T;
-                    ok = mbar_wait(BAR(B_VFULL + st), use & 1, ab, ST_WAIT_TIMEOUT + 5);
-                    if (ok && more) ok = k_ready(tp + 2);
-                    if (w == 0) FA_TRACE_EV(2, 3);
-                    if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 6);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (w == 0) FA_TRACE_EV(2, 4);
+                    for (int i = 0; i < nmine && ok; ++i, ++cw) {
+                        const int g = G + w + 2 * i, st = g % NS;
+                        const bool more = i + 1 < nmine;
+                        ok = mbar_wait(BAR(B_VFULL + st), (g / NS) & 1, ab, ST_WAIT_TIMEOUT + 5);
+                        if (ok && more) ok = k_ready(g + 2);
+                        // the first P*V of an item overwrites O: the previous item's epilogue must have read it
+                        if (ok && i == 0 && k > 0) ok = mbar_wait(BAR(B_OFREE + w), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 14);
+                        if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
+                        if (!ok) break;
+                        tc_fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv,
-                                (n_my > 0 || kk > 0) ? 1u : 0u);
-                    ok = mbar_wait(BAR(B_PHALF1 + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 6);
-                    if (!ok) break;
-                    tc_fence_after();
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv,
+                                    (i > 0 || kk > 0) ? 1u : 0u);
+                        ok = mbar_wait(BAR(B_PHALF1 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
+                        if (!ok) break;
+                        tc_fence_after();
 #pragma unroll
-                    for (int kk = 4; kk < 8; ++kk)
-                        umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv, 1u);
-                    umma_commit(BAR(B_VEMPTY + st));
-                    umma_commit(BAR(B_PVDONE + w));
-                    if (w == 0) FA_TRACE_EV(2, 5);
-                    if (more) s_mmas(tp + 2);
+                        for (int kk = 4; kk < 8; ++kk)
+                            umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv, 1u);
+                        umma_commit(BAR(B_VEMPTY + st));
+                        umma_commit(BAR(B_PVDONE + w));
+                        if (more) s_mmas(g + 2);
+                    }
+                    G += T;
+                    if (ok) mbar_arrive(BAR(B_ITEMEMPTY + s));
                 }
             }
         }
@@ -219,183 +316,227 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     } else {
         setmaxnreg_inc<216>();
         // ------------------------------ softmax groups ------------------------------
-        const int w = warp >> 2;           // group
-        const int r = tid & 127;           // row inside the block
+        // Every thread walks all items and takes part in both named barriers of every item, even
+        // after a wait has been given up (alive == false), so that no thread is ever left waiting.
+        const int w = warp >> 2;  // group
+        const int r = tid & 127;  // row inside the block
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-        const int row = qb * kBlk + r;
         const float c = p.scale_log2;
-        const int64_t bh_ids = int64_t(b) * mk.He + he;
-        const int qc = (mk.mode == 1) ? mk.plan[mk.L.off_qc + bh_ids * mk.L.Mpad + row] : 0;
-        float m_run = -INFINITY, l_run = 0.f;
-        int n_my = 0;
-        bool ok = !aborted;
         const uint32_t tS = tmem + lane_base + uint32_t(w) * 128u;
         const uint32_t tO = tmem + lane_base + 256u + uint32_t(w) * uint32_t(D);
+        bool alive = !aborted;
+        int k = 0, cw = 0;  // cw: tiles this group has finished (phases of its barriers)
+        int nturn = 0;      // turns this group has taken (phase of its turn barrier)
+        int G = 0;          // tiles of all earlier items (stage / phase of the K and V rings)
+        for (int j = blockIdx.x; j < n_items; j += gridDim.x, ++k) {
+            const int s = k & 1, use = k >> 1;
+            if (alive) {
+                alive = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
+                alive = __all_sync(0xffffffffu, alive);
+            }
+            const int T = alive ? info[s * 4 + 0] : 0;
+            const int lo = alive ? info[s * 4 + 1] : 0;
+            if (r == 0) FA_TRACE_EV(w, 32 + (T > 63 ? 63 : T));
+            const uint16_t* list = list_of(s);
+            int qb, h, b;
+            decode(j, qb, h, b);
+            const int row = qb * kBlk + r;
+            const int qc = reinterpret_cast<const int*>(smem + S::off_qc)[s * kBlk + r];
+            float m_run = -INFINITY, l_run = 0.f;
+            int n_my = 0;
+            const int n_other = (w == 0) ? T / 2 : (T + 1) / 2;  // tiles of the other group
+            // short items: both groups simply run side by side; long items: the exp phase is taken in turns
+            const bool turns = T >= kTurnMinTiles;
+            if (turns && w == 1 && alive) mbar_arrive(BAR(B_TURN + 0));  // group 0 takes the first turn
 
-        const int n_other = (w == 0) ? T / 2 : (T + 1) / 2;  // tiles of the other group
-        if (w == 1 && T > 0 && ok) mbar_arrive(BAR(B_TURN + 0));  // group 0 takes the first turn
-        for (int t = w; t < T && ok; t += 2, ++n_my) {
-            const uint32_t entry = list[t];
-            const uint32_t fl = entry >> 10;
-            const int k0 = (lo + int(entry & 1023u)) * kBlk;
-            if (r == 0) FA_TRACE_EV(w, 10);
-            ok = mbar_wait(BAR(B_SFULL + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 7);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            if (r == 0) FA_TRACE_EV(w, 11);
-            uint32_t sr[128];
+            for (int t = w; t < T && alive; t += 2, ++n_my, ++cw) {
+                const uint32_t entry = list[t];
+                const uint32_t fl = entry >> 10;
+                const int k0 = (lo + int(entry & 1023u)) * kBlk;
+                alive = mbar_wait(BAR(B_SFULL + w), cw & 1, ab, ST_WAIT_TIMEOUT + 7);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                tc_fence_after();
+                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 5);
+                uint32_t sr[128];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) tmem_ld32(tS + uint32_t(q) * 32u, sr + q * 32);
-            tc_wait_ld();
-            float* s = reinterpret_cast<float*>(sr);
-            if (r == 0) FA_TRACE_EV(w, 12);
+                for (int q = 0; q < 4; ++q) tmem_ld32(tS + uint32_t(q) * 32u, sr + q * 32);
+                tc_wait_ld();
+                float* sc = reinterpret_cast<float*>(sr);
+                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 6);
 
-            if (fl & (TILE_BOUND | TILE_DOC)) {
-                int lim = kBlk - 1;
-                if (fl & TILE_BOUND) {
-                    int jmax = mk.N - 1;
-                    if (mk.causal) jmax = min(jmax, row + mk.gap);
-                    lim = jmax - k0;
-                }
-                if ((fl & TILE_DOC) && qc < 0) {
-                    const int4* kc4 = reinterpret_cast<const int4*>(mk.plan + mk.L.off_kc + bh_ids * mk.L.Npad + k0);
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) {
-                        const int4 kc = __ldg(kc4 + q);
-                        s[4 * q + 0] = (kc.x == qc && 4 * q + 0 <= lim) ? s[4 * q + 0] : -INFINITY;
-                        s[4 * q + 1] = (kc.y == qc && 4 * q + 1 <= lim) ? s[4 * q + 1] : -INFINITY;
-                        s[4 * q + 2] = (kc.z == qc && 4 * q + 2 <= lim) ? s[4 * q + 2] : -INFINITY;
-                        s[4 * q + 3] = (kc.w == qc && 4 * q + 3 <= lim) ? s[4 * q + 3] : -INFINITY;
+                if (fl & (TILE_BOUND | TILE_DOC)) {
+                    // keep(x) = (x <= lim) & (qc >= 0 | kc[x] == qc). The compare + select per entry is
+                    // ALU work that costs as much as the tile's MMAs, so it is done per 32-key chunk
+                    // where possible: a chunk is kept or masked as a whole when it lies entirely on
+                    // one side of the bound and (for monotone key codes) holds one single document.
+                    int lim = kBlk - 1;
+                    if (fl & TILE_BOUND) {
+                        int jmax = mk.N - 1;
+                        if (mk.causal) jmax = min(jmax, row + mk.gap);
+                        lim = jmax - k0;
                     }
-                } else {
+                    const bool doc = (fl & TILE_DOC) && qc < 0;  // a row with qc >= 0 passes the id check everywhere
+                    const int* kcs = reinterpret_cast<const int*>(smem + S::off_kc + ((G + t) % S::NKC) * (kBlk * 4));
+                    if (fl & TILE_DOC) {  // the key codes were fetched together with the K tile
+                        const int g = G + t;
+                        alive = mbar_wait(BAR(B_KCFULL + g % S::NKC), (g / S::NKC) & 1, ab, ST_WAIT_TIMEOUT + 15);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                    }
+                    if (r == 0 && n_my == 0) FA_TRACE_EV(w, 11);
 #pragma unroll
-                    for (int j = 0; j < 128; ++j) s[j] = (j <= lim) ? s[j] : -INFINITY;
+                    for (int q = 0; q < 4; ++q) {
+                        int state = 0;  // this row in chunk q: 0 keep all, 1 mask all, 2 entry by entry
+                        if (32 * q > lim) state = 1;
+                        else if (32 * q + 31 > lim) state = 2;
+                        if (doc && state != 1) {
+                            if (fl & TILE_KMONO) {
+                                const int kf = kcs[32 * q], kl = kcs[32 * q + 31];
+                                if (kf != kl) state = 2;
+                                else if (kf != qc) state = 1;
+                            } else {
+                                state = 2;
+                            }
+                        }
+                        if (!__any_sync(0xffffffffu, state == 2)) {
+                            if (state == 1) {
+#pragma unroll
+                                for (int x = 0; x < 32; ++x) sc[32 * q + x] = -INFINITY;
+                            }
+                        } else if (doc) {
+                            const int4* kc4 = reinterpret_cast<const int4*>(kcs + 32 * q);
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int4 kc = kc4[u];
+                                const int x = 32 * q + 4 * u;
+                                sc[x + 0] = (kc.x == qc && x + 0 <= lim) ? sc[x + 0] : -INFINITY;
+                                sc[x + 1] = (kc.y == qc && x + 1 <= lim) ? sc[x + 1] : -INFINITY;
+                                sc[x + 2] = (kc.z == qc && x + 2 <= lim) ? sc[x + 2] : -INFINITY;
+                                sc[x + 3] = (kc.w == qc && x + 3 <= lim) ? sc[x + 3] : -INFINITY;
+                            }
+                        } else {
+#pragma unroll
+                            for (int x = 0; x < 32; ++x) sc[32 * q + x] = (32 * q + x <= lim) ? sc[32 * q + x] : -INFINITY;
+                        }
+                    }
                 }
-            }
-            if (r == 0) FA_TRACE_EV(w, 18);
-            float mxa[8];
+                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 7);
+                float mxa[8];
 #pragma unroll
-            for (int a = 0; a < 8; ++a) mxa[a] = max3(s[a], s[8 + a], s[16 + a]);
+                for (int a = 0; a < 8; ++a) mxa[a] = max3(sc[a], sc[8 + a], sc[16 + a]);
 #pragma unroll
-            for (int j = 24; j < 120; j += 16) {
+                for (int x = 24; x < 120; x += 16) {
 #pragma unroll
-                for (int a = 0; a < 8; ++a) mxa[a] = max3(mxa[a], s[j + a], s[j + 8 + a]);
-            }
+                    for (int a = 0; a < 8; ++a) mxa[a] = max3(mxa[a], sc[x + a], sc[x + 8 + a]);
+                }
 #pragma unroll
-            for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], s[120 + a]);
-            const float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), max3(max3(mxa[3], mxa[4], mxa[5]), mxa[6], mxa[7]));
-            if (r == 0) FA_TRACE_EV(w, 19);
-            float m_new = fmaxf(m_run, mx);
-            // lazy rescale: keep the old reference point while the new maximum is within 2^8 of it
-            const bool need = (m_new - m_run) * c > 8.0f;
-            if (!need) m_new = m_run;
-            if (__any_sync(0xffffffffu, need)) {
-                const float alpha = need ? fast_exp2((m_run - m_new) * c) : 1.0f;
-                l_run *= alpha;
-                if (n_my > 0) {
-                    ok = mbar_wait(BAR(B_PVDONE + w), (n_my - 1) & 1, ab, ST_WAIT_TIMEOUT + 8);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
+                for (int a = 0; a < 8; ++a) mxa[a] = fmaxf(mxa[a], sc[120 + a]);
+                const float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), max3(max3(mxa[3], mxa[4], mxa[5]), mxa[6], mxa[7]));
+                float m_new = fmaxf(m_run, mx);
+                // lazy rescale: keep the old reference point while the new maximum is within 2^8 of it
+                const bool need = (m_new - m_run) * c > 8.0f;
+                if (!need) m_new = m_run;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float alpha = need ? fast_exp2((m_run - m_new) * c) : 1.0f;
+                    l_run *= alpha;
+                    if (n_my > 0) {
+                        alive = mbar_wait(BAR(B_PVDONE + w), (cw - 1) & 1, ab, ST_WAIT_TIMEOUT + 8);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                        tc_fence_after();
 #pragma unroll
-                    for (int q = 0; q < D / 32; ++q) {
-                        uint32_t orr[32];
-                        tmem_ld32(tO + uint32_t(q) * 32u, orr);
-                        tc_wait_ld();
+                        for (int q = 0; q < D / 32; ++q) {
+                            uint32_t orr[32];
+                            tmem_ld32(tO + uint32_t(q) * 32u, orr);
+                            tc_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
-                        tmem_st32(tO + uint32_t(q) * 32u, orr);
+                            for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
+                            tmem_st32(tO + uint32_t(q) * 32u, orr);
+                        }
+                        tc_wait_st();
+                    }
+                }
+                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 8);
+                m_run = m_new;
+                const float mneg = (m_run == -INFINITY) ? 0.f : -m_run * c;
+                // exp2(s*c - m*c) on packed pairs; P goes to TMEM in two halves so that the first four
+                // k-steps of P*V can start while the second half is still being exponentiated. MUFU
+                // (16 ex2 per clock and SM) is as scarce as the tensor pipe here, so on tiles without
+                // masked entries kPolyOf4 of every 4 pairs are evaluated on the FMA pipe instead.
+                const uint64_t c2 = pack_f2(c, c), mneg2 = pack_f2(mneg, mneg);
+                uint64_t lacc0 = pack_f2(0.f, 0.f), lacc1 = lacc0;
+                // The exp phase is taken in turns (barriers turn[0], turn[1]; group 0 first): left alone,
+                // the groups fall into lockstep, exponentiate together at half MUFU rate each and then
+                // queue their MMAs together, which halves the use of both pipes. In turns, one group
+                // exponentiates while the other group's P*V and next S run on the tensor pipe.
+                if (turns) {
+                    alive = mbar_wait(BAR(B_TURN + w), nturn & 1, ab, ST_WAIT_TIMEOUT + 10);
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    ++nturn;
+                }
+                const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
+                auto exp_half = [&](auto use_poly, int half) {
+#pragma unroll
+                    for (int q = 2 * half; q < 2 * half + 2; ++q) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) {
+                            const uint64_t x2 = fma_f2(pack_f2(sc[32 * q + 2 * x], sc[32 * q + 2 * x + 1]), c2, mneg2);
+                            float p0, p1;
+                            if (decltype(use_poly)::value && (x & 3) < kPolyOf4) {
+                                exp2_poly2(x2, p0, p1);
+                            } else {
+                                float x0, x1;
+                                unpack_f2(x2, x0, x1);
+                                p0 = fast_exp2(x0);
+                                p1 = fast_exp2(x1);
+                            }
+                            if (x & 1) lacc1 = add_f2(lacc1, pack_f2(p0, p1)); else lacc0 = add_f2(lacc0, pack_f2(p0, p1));
+                            pk[x] = pack2<BF16>(p0, p1);
+                        }
+                        tmem_st16(tS + uint32_t(q) * 16u, pk);
                     }
                     tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(BAR((half ? B_PHALF1 : B_PHALF0) + w));
+                    if (r == 0 && n_my == 0) FA_TRACE_EV(w, 9 + half);
+                };
+                if (poly_ok) {
+                    exp_half(std::true_type{}, 0);
+                    exp_half(std::true_type{}, 1);
+                } else {
+                    exp_half(std::false_type{}, 0);
+                    exp_half(std::false_type{}, 1);
+                }
+                // hand the turn over, unless the other group has no tile left to take it for
+                if (turns && (w == 0 ? (n_my < n_other) : (n_my + 1 < n_other))) mbar_arrive(BAR(B_TURN + (w ^ 1)));
+                {
+                    float a0, a1, b0, b1;
+                    unpack_f2(lacc0, a0, a1);
+                    unpack_f2(lacc1, b0, b1);
+                    l_run += (a0 + a1) + (b0 + b1);
                 }
             }
-            if (r == 0) FA_TRACE_EV(w, 13);
-            m_run = m_new;
-            const float mneg = (m_run == -INFINITY) ? 0.f : -m_run * c;
-            // exp2(s*c - m*c) on packed pairs; P goes to TMEM in two halves so that the first four
-            // k-steps of P*V can start while the second half is still being exponentiated. MUFU
-            // (16 ex2 per clock and SM) is as scarce as the tensor pipe here, so on tiles without
-            // masked entries kPolyOf4 of every 4 pairs are evaluated on the FMA pipe instead.
-            const uint64_t c2 = pack_f2(c, c), mneg2 = pack_f2(mneg, mneg);
-            uint64_t lacc0 = pack_f2(0.f, 0.f), lacc1 = lacc0;
-            // The exp phase is taken in turns (barriers turn[0], turn[1]; group 0 first): left alone,
-            // the groups fall into lockstep, exponentiate together at half MUFU rate each and then
-            // queue their MMAs together, which halves the use of both pipes. In turns, one group
-            // exponentiates while the other group's P*V and next S run on the tensor pipe.
-            ok = mbar_wait(BAR(B_TURN + w), n_my & 1, ab, ST_WAIT_TIMEOUT + 10);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
-            auto exp_half = [&](auto use_poly, int half) {
-#pragma unroll
-                for (int q = 2 * half; q < 2 * half + 2; ++q) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const uint64_t x2 = fma_f2(pack_f2(s[32 * q + 2 * j], s[32 * q + 2 * j + 1]), c2, mneg2);
-                        float p0, p1;
-                        if (decltype(use_poly)::value && (j & 3) < kPolyOf4) {
-                            exp2_poly2(x2, p0, p1);
-                        } else {
-                            float x0, x1;
-                            unpack_f2(x2, x0, x1);
-                            p0 = fast_exp2(x0);
-                            p1 = fast_exp2(x1);
-                        }
-                        if (j & 1) lacc1 = add_f2(lacc1, pack_f2(p0, p1)); else lacc0 = add_f2(lacc0, pack_f2(p0, p1));
-                        pk[j] = pack2<BF16>(p0, p1);
-                    }
-                    tmem_st16(tS + uint32_t(q) * 16u, pk);
-                }
-                tc_wait_st();
-                tc_fence_before();
-                mbar_arrive(BAR((half ? B_PHALF1 : B_PHALF0) + w));
-                if (r == 0) FA_TRACE_EV(w, 14 + half);
-            };
-            if (poly_ok) {
-                exp_half(std::true_type{}, 0);
-                exp_half(std::true_type{}, 1);
-            } else {
-                exp_half(std::false_type{}, 0);
-                exp_half(std::false_type{}, 1);
-            }
-            // hand the turn over, unless the other group has no tile left to take it for
-            if (w == 0 ? (n_my < n_other) : (n_my + 1 < n_other)) mbar_arrive(BAR(B_TURN + (w ^ 1)));
-            {
-                float a0, a1, b0, b1;
-                unpack_f2(lacc0, a0, a1);
-                unpack_f2(lacc1, b0, b1);
-                l_run += (a0 + a1) + (b0 + b1);
-            }
-            if (r == 0) FA_TRACE_EV(w, 15);
-        }
 
-        // ------------------------------ epilogue ------------------------------
-        // wait for this group's last P*V, then merge the two partial softmaxes
-        if (ok && n_my > 0) {
-            ok = mbar_wait(BAR(B_PVDONE + w), (n_my - 1) & 1, ab, ST_WAIT_TIMEOUT + 9);
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        // Group 0 owns tile 0, so once both groups have passed this barrier every MMA of the CTA
-        // has completed and the Q tile may be reused as the exchange buffer. (A group without
-        // tiles gets here at once; it must not touch Q before the barrier.)
-        tc_fence_before();
-        named_bar_sync(1, 256);
-        tc_fence_after();
-        float* ml = reinterpret_cast<float*>(smem + S::off_q);  // [2 groups][m, l][128]
-        if (T > 0 && !aborted) {
-            ml[(w * 2 + 0) * 128 + r] = m_run;
-            ml[(w * 2 + 1) * 128 + r] = l_run;
-        }
-        named_bar_sync(1, 256);
-        const bool healthy = ok && (misc[1] == 0);
-        if (healthy) {
-            float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-            if (T > 0) {
-                m0 = ml[0 * 128 + r]; l0 = ml[1 * 128 + r];
-                m1 = ml[2 * 128 + r]; l1 = ml[3 * 128 + r];
+            // ------------------------------ item epilogue ------------------------------
+            // wait for this group's last P*V, then merge the two partial softmaxes
+            if (r == 0) FA_TRACE_EV(w, 1);
+            if (alive && n_my > 0) {
+                alive = mbar_wait(BAR(B_PVDONE + w), (cw - 1) & 1, ab, ST_WAIT_TIMEOUT + 9);
+                alive = __all_sync(0xffffffffu, alive);
             }
+            float* ml = reinterpret_cast<float*>(smem + S::off_ml) + s * (4 * kBlk);  // [2 groups][m, l][128]
+            ml[(w * 2 + 0) * kBlk + r] = m_run;
+            ml[(w * 2 + 1) * kBlk + r] = l_run;
+            if (r == 0) FA_TRACE_EV(w, 2);
+            tc_fence_before();
+            named_bar_sync(1, 256);  // both groups are past all MMAs of this item
+            tc_fence_after();
+            if (r == 0) FA_TRACE_EV(w, 3);
+            const float m0 = ml[0 * kBlk + r], l0 = ml[1 * kBlk + r];
+            const float m1 = ml[2 * kBlk + r], l1 = ml[3 * kBlk + r];
             const float mt = fmaxf(m0, m1);
             const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2((m0 - mt) * c);
             const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2((m1 - mt) * c);
@@ -403,14 +544,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const float inv = (lt > 0.f) ? 1.0f / lt : 0.f;
             const float f0 = a0 * inv, f1 = a1 * inv;
             const bool use0 = (T > 0) && (f0 != 0.f), use1 = (T > 1) && (f1 != 0.f);
-            if (w == 0) {
+            const bool healthy = alive && (misc[1] == 0);
+            if (w == 0 && healthy) {
                 const float lse = (lt > 0.f) ? fmaf(mt, c, log2f(lt)) : -INFINITY;
                 p.lse[(int64_t(b) * p.H + h) * mk.L.Mpad + row] = lse;
             }
+            // this thread's half row: O0 and O1 columns [w*D/2, (w+1)*D/2)
             constexpr int HALF = D / 2;
             const uint32_t c0 = uint32_t(w) * HALF;
-            uint8_t* orow = static_cast<uint8_t*>(p.o.ptr) +
-                            2 * (int64_t(b) * p.o.sb + int64_t(h) * p.o.sh + int64_t(row) * p.o.sl + c0);
+            uint32_t outw[HALF / 2];
 #pragma unroll
             for (int q = 0; q < HALF / 32; ++q) {
                 uint32_t x0[32], x1[32];
@@ -418,26 +560,44 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 tmem_ld32(tmem + lane_base + 256u + c0 + uint32_t(q) * 32u, x0);
                 tmem_ld32(tmem + lane_base + 256u + uint32_t(D) + c0 + uint32_t(q) * 32u, x1);
                 tc_wait_ld();
-                uint32_t out[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int x = 0; x < 16; ++x) {
                     float v0 = 0.f, v1 = 0.f;
                     if (use0) {
-                        v0 = __uint_as_float(x0[2 * j]) * f0;
-                        v1 = __uint_as_float(x0[2 * j + 1]) * f0;
+                        v0 = __uint_as_float(x0[2 * x]) * f0;
+                        v1 = __uint_as_float(x0[2 * x + 1]) * f0;
                     }
                     if (use1) {
-                        v0 = fmaf(__uint_as_float(x1[2 * j]), f1, v0);
-                        v1 = fmaf(__uint_as_float(x1[2 * j + 1]), f1, v1);
+                        v0 = fmaf(__uint_as_float(x1[2 * x]), f1, v0);
+                        v1 = fmaf(__uint_as_float(x1[2 * x + 1]), f1, v1);
                     }
-                    out[j] = pack2<BF16>(v0, v1);
-                }
-                if (row < mk.M) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + q * 64);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                    outw[16 * q + x] = pack2<BF16>(v0, v1);
                 }
             }
+            // both accumulators have been read: the MMA issuers may start the next item's P*V
+            tc_fence_before();
+            if (alive) {
+                mbar_arrive(BAR(B_OFREE + 0));
+                mbar_arrive(BAR(B_OFREE + 1));
+            }
+            // Stage the O tile in this item's Q slot (Q is dead: every S MMA of the item has
+            // completed) in the 128-byte-swizzled layout of the tensor map; the producer warp issues
+            // the TMA store when every thread has arrived, and reuses the slot once it has been read.
+            {
+                uint8_t* stage = smem + S::off_q + s * S::TILE;
+#pragma unroll
+                for (int i = 0; i < HALF / 8; ++i) {
+                    const int cg = int(c0) / 8 + i;  // 16-byte chunk of the row
+                    const int box = cg >> 3, ch = cg & 7;
+                    uint4* dst = reinterpret_cast<uint4*>(stage + box * S::BOX + r * 128 + ((ch ^ (r & 7)) << 4));
+                    *dst = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+                }
+            }
+            fence_proxy_async();
+            if (healthy) mbar_arrive(BAR(B_OSTAGED + s));  // the producer warp issues the TMA store
+            G += T;
+            if (r == 0 && alive) mbar_arrive(BAR(B_ITEMEMPTY + s));
+            if (r == 0) FA_TRACE_EV(w, 4);
         }
     }
 
@@ -453,23 +613,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 // ---- host launcher (called from api.cu) -------------------------------------------------
 template <int D, bool BF16>
 static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                const FwdParams& p, int B, cudaStream_t stream) {
+                                const CUtensorMap& to, const FwdParams& p, int num_sms, cudaStream_t stream) {
     auto kern = fwd_kernel<D, BF16>;
     constexpr int smem = FwdSmem<D>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    dim3 grid(p.mask.L.nQ, p.H, B);
-    kern<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, p);
+    const int n_items = p.mask.L.nQ * p.H * p.B;
+    dim3 grid(n_items < num_sms ? n_items : num_sms);
+    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, to, p);
     return cudaGetLastError();
 }
 
 FA_TRACE_DUMP_FN(fa_trace_dump_fwd)
 
 cudaError_t launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                       const FwdParams& p, int B, cudaStream_t stream) {
-    if (D == 128) return bf16 ? launch_fwd_t<128, true>(tq, tk, tv, p, B, stream)
-                              : launch_fwd_t<128, false>(tq, tk, tv, p, B, stream);
-    return bf16 ? launch_fwd_t<64, true>(tq, tk, tv, p, B, stream) : launch_fwd_t<64, false>(tq, tk, tv, p, B, stream);
+                       const CUtensorMap& to, const FwdParams& p, int num_sms, cudaStream_t stream) {
+    if (D == 128) return bf16 ? launch_fwd_t<128, true>(tq, tk, tv, to, p, num_sms, stream)
+                              : launch_fwd_t<128, false>(tq, tk, tv, to, p, num_sms, stream);
+    return bf16 ? launch_fwd_t<64, true>(tq, tk, tv, to, p, num_sms, stream)
+                : launch_fwd_t<64, false>(tq, tk, tv, to, p, num_sms, stream);
 }
 
 }  // namespace fa

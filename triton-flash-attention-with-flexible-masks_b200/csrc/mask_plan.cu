@@ -73,7 +73,20 @@ __global__ void __launch_bounds__(128) plan_codes_kernel(IdsView eq, IdsView ek,
     }
     const int mn = block_reduce_min(valid ? code : 0x7fffffff, scratch);
     const int mx = block_reduce_max(valid ? code : int(-2147483647 - 1), scratch);
+    // monotone within the block (valid entries): no rise or no fall between neighbours
+    __shared__ int codes[kBlk];
+    codes[threadIdx.x] = code;
+    __syncthreads();
+    int rise = 0, fall = 0;
+    if (valid && threadIdx.x > 0) {
+        rise = code > codes[threadIdx.x - 1];
+        fall = code < codes[threadIdx.x - 1];
+    }
+    const int any_rise = block_reduce_max(rise, scratch);
+    const int any_fall = block_reduce_max(fall, scratch);
+    const int mono = !(any_rise && any_fall);
     if (threadIdx.x == 0) {
+        plan[(is_q ? L.off_qmono + bh * L.nQ : L.off_kmono + bh * L.nK) + blk] = mono;
         if (is_q) {
             plan[L.off_qmin + bh * L.nQ + blk] = mn;
             plan[L.off_qmax + bh * L.nQ + blk] = mx;

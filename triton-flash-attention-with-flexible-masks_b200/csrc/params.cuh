@@ -9,10 +9,9 @@ constexpr int kFwdThreads = kAttnThreads;
 constexpr int kListCap = 1024;     // blocks per sequence (visited-tile lists live in shared memory)
 
 struct FwdParams {
-    OutTensor o;
     float* lse;  // [B, H, Mpad], log2 domain
     MaskArgs mask;
-    int H, G;
+    int H, B, G;
     float scale_log2;  // sm_scale * log2(e)
     int* status;
 };

@@ -80,6 +80,7 @@ struct Abort {
 // Returns false when the wait was abandoned (limit reached here, or another role gave up).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Abort& ab, int code) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*ab.flag) return false;  // another role already gave up: drain quickly
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -108,6 +109,18 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// tile store shared -> global (rows outside the tensor are clipped by the map)
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores have finished READING shared memory (it may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed stores are complete
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile(
