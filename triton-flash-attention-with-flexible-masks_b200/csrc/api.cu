@@ -13,9 +13,10 @@ cudaError_t launch_fwd(int, bool, const CUtensorMap&, const CUtensorMap&, const 
                        const FwdParams&, int, cudaStream_t);
 cudaError_t launch_bwd_delta(const DeltaParams&, cudaStream_t);
 cudaError_t launch_bwd_dkdv(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
-                            const CUtensorMap&, const DkdvParams&, int, cudaStream_t);
+                            const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const DkdvParams&, int,
+                            cudaStream_t);
 cudaError_t launch_bwd_dq(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
-                          const CUtensorMap&, const DqParams&, int, cudaStream_t);
+                          const CUtensorMap&, const CUtensorMap&, const DqParams&, int, cudaStream_t);
 }  // namespace fa
 
 namespace {
@@ -240,8 +241,9 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     if ((rc = make_map(&tdo, d_o, p->dtype, p->B, p->H, p->M, p->D))) return rc;
     if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
-    kp.dk = out_view(dk);
-    kp.dv = out_view(dv);
+    CUtensorMap tdk, tdv;
+    if ((rc = make_map(&tdk, dk, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    if ((rc = make_map(&tdv, dv, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     kp.lse = lse;
     kp.delta = delta;
     kp.H = p->H;
@@ -251,7 +253,8 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     kp.sm_scale = p->sm_scale;
     kp.status = status;
     const cudaError_t e =
-        fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, kp, p->B, static_cast<cudaStream_t>(stream));
+        fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdk, tdv, kp, p->B,
+                            static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
 }
 
@@ -273,7 +276,8 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     if ((rc = make_map(&tdo, d_o, p->dtype, p->B, p->H, p->M, p->D))) return rc;
     if ((rc = make_map(&tk, k, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
-    qp.dq = out_view(dq);
+    CUtensorMap tdq;
+    if ((rc = make_map(&tdq, dq, p->dtype, p->B, p->H, p->M, p->D))) return rc;
     qp.lse = lse;
     qp.delta = delta;
     qp.H = p->H;
@@ -282,7 +286,7 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     qp.sm_scale = p->sm_scale;
     qp.status = status;
     const cudaError_t e =
-        fa::launch_bwd_dq(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, qp, p->B, static_cast<cudaStream_t>(stream));
+        fa::launch_bwd_dq(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdq, qp, p->B, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
 }
 

@@ -3,13 +3,17 @@
 // query head of the group, recompute P, and accumulate dV += P^T dO, dK += dS^T Q in fp32.
 //
 // The tile is kept transposed (rows = keys, columns = queries): S^T = K Q^T and dP^T = V dO^T
-// land in TMEM with one key per lane, so P^T and dS^T (input dtype) can be written back to
-// TMEM and used directly as the A operand of the dV / dK MMAs, with dO / Q read from shared
-// memory as MN-major B operands. One CTA = one key block of one (batch, kv head), 12 warps:
+// land in TMEM with one key per lane. P^T (input dtype) is written to a shared-memory tile in the
+// K-major swizzled layout and is the A operand of dV += P^T dO; because it does not live in the
+// S^T columns, S^T of the next tile is issued as soon as the scores have been read into
+// registers and overlaps the whole exp / mask phase. dS^T goes back to TMEM over dP^T and is the
+// A operand of dK += dS^T Q. dO and Q are read as MN-major B operands from their TMA tiles.
+// One CTA = one key block of one (batch, kv head), 12 warps:
 //   warps 0-7  two compute groups; thread r of group g owns key row r and query columns
 //              [64g, 64g+64) of every tile
-//   warp 8     TMA producer (K, V once; Q ring with the per-row LSE / delta / id codes; dO ring)
-//   warps 9,10 tcgen05.mma issuers (warp 9 also owns the TMEM allocation)
+//   warp 8     TMA producer (K, V once; Q ring with the per-row LSE / delta; dO ring)
+//   warp 9     tcgen05.mma issuer for S^T
+//   warp 10    tcgen05.mma issuer for dV, dK and dP^T; warp 9 also owns the TMEM allocation
 // TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [256+D,256+2D).
 #include "common.cuh"
 #include "params.cuh"
@@ -19,23 +23,30 @@ namespace fa {
 
 template <int D>
 struct DkdvSmem {
-    static constexpr int NST = (D == 128) ? 2 : 4;
+    static constexpr int NST = (D == 128) ? 2 : 3;
     static constexpr int TILE = kBlk * D * 2;
     static constexpr int BOX = kBlk * 64 * 2;
     static constexpr int NBOX = D / 64;
-    static constexpr int VEC = 3 * kBlk * 4;  // lse, delta, query codes of one query block
+    static constexpr int PT = kBlk * kBlk * 2;  // P^T tile: 128 keys x 128 queries
+    static constexpr int VEC = 2 * kBlk * 4;    // lse, delta of one query block
     static constexpr int off_k = 0;
     static constexpr int off_v = TILE;
     static constexpr int off_q = 2 * TILE;
     static constexpr int off_do = off_q + NST * TILE;
-    static constexpr int off_vec = off_do + NST * TILE;
-    static constexpr int off_list = off_vec + NST * VEC;
-    static constexpr int off_bar = off_list + kListCap * 2;
-    // kv_full, q_full[NST], do_full[NST], q_empty[NST], do_empty[NST], s_full, dp_full, p_full, ds_full, done
-    static constexpr int n_bar = 1 + 4 * NST + 5;
+    static constexpr int off_p = off_do + NST * TILE;
+    static constexpr int off_vec = off_p + PT;
+    static constexpr int off_flags = off_vec + NST * VEC;  // 4 bits per candidate query block
+    static constexpr int off_bar = off_flags + kListCap / 2;
+    // kv_full, q_full[NST], do_full[NST], q_empty[NST], do_empty[NST],
+    // s_full, s_free, dp_full, p_full, p_free, ds_full, done
+    static constexpr int n_bar = 1 + 4 * NST + 7;
     static constexpr int off_misc = off_bar + n_bar * 8;
     static constexpr int total = off_misc + 16;
 };
+
+// Per-candidate flags kept in shared memory (4 bits): visited, range check (causal bound and / or
+// query tail), id check, query codes of the block monotone.
+enum : uint32_t { KF_VISIT = 1u, KF_RANGE = 2u, KF_DOC = 4u, KF_QMONO = 8u };
 
 // Flags of tile (qb, kb) for all query heads of one kv head at once. When the heads disagree
 // (ids given per head) the id check is forced, which is always exact.
@@ -55,6 +66,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
                 const DkdvParams p) {
     using S = DkdvSmem<D>;
     constexpr int NST = S::NST;
@@ -68,13 +80,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int hk = blockIdx.y, b = blockIdx.z;
     const int G = p.G;
 
-    uint16_t* list = reinterpret_cast<uint16_t*>(smem + S::off_list);
+    uint8_t* flags = smem + S::off_flags;
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);
     const uint32_t bar0 = sbase + S::off_bar;
     auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
     const int B_KV = 0, B_QFULL = 1, B_DOFULL = B_QFULL + NST, B_QEMPTY = B_DOFULL + NST, B_DOEMPTY = B_QEMPTY + NST,
-              B_SFULL = B_DOEMPTY + NST, B_DPFULL = B_SFULL + 1, B_PFULL = B_SFULL + 2, B_DSFULL = B_SFULL + 3,
-              B_DONE = B_SFULL + 4;
+              B_SFULL = B_DOEMPTY + NST, B_SFREE = B_SFULL + 1, B_DPFULL = B_SFULL + 2, B_PFULL = B_SFULL + 3,
+              B_PFREE = B_SFULL + 4, B_DSFULL = B_SFULL + 5, B_DONE = B_SFULL + 6;
     Abort ab{misc + 1, p.status};
 
     // union of the query-block ranges of the group's heads
@@ -95,11 +107,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(BAR(B_KV), 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(BAR(B_QFULL + s), 1); mbar_init(BAR(B_DOFULL + s), 1);
-            mbar_init(BAR(B_QEMPTY + s), 2); mbar_init(BAR(B_DOEMPTY + s), 2);  // one commit per MMA issuer
+            mbar_init(BAR(B_QEMPTY + s), 2);  // S^T (warp 9) and dK (warp 10) both read the Q stage
+            mbar_init(BAR(B_DOEMPTY + s), 1); // dP^T and dV are issued by the same thread: one commit
         }
         mbar_init(BAR(B_SFULL), 1);
+        mbar_init(BAR(B_SFREE), 256);
         mbar_init(BAR(B_DPFULL), 1);
         mbar_init(BAR(B_PFULL), 256);
+        mbar_init(BAR(B_PFREE), 1);
         mbar_init(BAR(B_DSFULL), 256);
         mbar_init(BAR(B_DONE), 2);
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
@@ -110,13 +125,32 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_alloc(sbase + S::off_misc, 512);
         tmem_relinquish();
     }
-    for (int i = tid; i < n; i += kAttnThreads) list[i] = uint16_t(classify_group(mk, b, hk, G, lo + i, kb));
+    // flags of the candidate query blocks [lo, lo+n), two per byte
+    for (int i = tid; 2 * i < n; i += kAttnThreads) {
+        uint32_t byte = 0;
+        for (int e = 0; e < 2; ++e) {
+            const int c = 2 * i + e;
+            if (c >= n) break;
+            const uint32_t f = classify_group(mk, b, hk, G, lo + c, kb);
+            uint32_t kf = 0;
+            if (f & TILE_VISIT) {
+                kf = KF_VISIT;
+                if (((f & TILE_BOUND) && mk.causal) || (f & TILE_QTAIL)) kf |= KF_RANGE;
+                if (f & TILE_DOC) kf |= KF_DOC;
+                if (f & TILE_QMONO) kf |= KF_QMONO;
+            }
+            byte |= kf << (4 * e);
+        }
+        flags[i] = uint8_t(byte);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) {
-        const int Tn = compact_visit_list(list, n, lane);
-        if (lane == 0) misc[2] = Tn;
+    if (warp == 0) {  // number of visited candidates
+        int cnt = 0;
+        for (int i = lane; 2 * i < n; i += 32) cnt += (flags[i] & KF_VISIT) + ((flags[i] >> 4) & KF_VISIT);
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        if (lane == 0) misc[2] = cnt;
     }
     __syncthreads();
     const uint32_t tmem = uint32_t(misc[0]);
@@ -124,7 +158,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int NIT = T * G;  // tiles of all query heads of the group, head-major
     const bool aborted = misc[1] != 0;
 
-    const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v;
+    auto flag_of = [&](int c) { return (uint32_t(flags[c >> 1]) >> (4 * (c & 1))) & 15u; };
+    // walks the visited candidates of all heads: (g, c) -> next visited; c == n means "past the end"
+    struct Cursor { int g, c; };
+    auto first_from = [&](int c) { while (c < n && !(flag_of(c) & KF_VISIT)) ++c; return c; };
+    auto advance = [&](Cursor& cur) {
+        cur.c = first_from(cur.c + 1);
+        if (cur.c >= n) { cur.g += 1; cur.c = first_from(0); }
+    };
+
+    const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v, sP = sbase + S::off_p;
     auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
     auto sdO = [&](int s) { return sbase + S::off_do + uint32_t(s) * S::TILE; };
     auto sVec = [&](int s) { return sbase + S::off_vec + uint32_t(s) * S::VEC; };
@@ -142,25 +185,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tma_load_4d(sV + x * S::BOX, &tmV, BAR(B_KV), x * 64, kb * kBlk, hk, b);
                 }
                 bool ok = true;
-                const uint32_t vec_bytes = (mk.mode == 1) ? 3u * kBlk * 4u : 2u * kBlk * 4u;
-                for (int it = 0; it < NIT && ok; ++it) {
-                    const int g = it / T, idx = it - g * T;
-                    const int h = hk * G + g;
-                    const int qb = lo + (list[idx] & 1023);
+                Cursor cur{0, first_from(0)};
+                for (int it = 0; it < NIT && ok; ++it, advance(cur)) {
+                    const int h = hk * G + cur.g;
+                    const int qb = lo + cur.c;
                     const int st = it % NST, use = it / NST;
                     if (use > 0) ok = mbar_wait(BAR(B_QEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 41);
                     if (!ok) break;
-                    mbar_expect_tx(BAR(B_QFULL + st), S::TILE + vec_bytes);
+                    mbar_expect_tx(BAR(B_QFULL + st), S::TILE + S::VEC);
                     for (int x = 0; x < S::NBOX; ++x)
                         tma_load_4d(sQ(st) + x * S::BOX, &tmQ, BAR(B_QFULL + st), x * 64, qb * kBlk, h, b);
                     const int64_t roff = (int64_t(b) * p.H + h) * mk.L.Mpad + int64_t(qb) * kBlk;
                     bulk_load_1d(sVec(st), p.lse + roff, kBlk * 4, BAR(B_QFULL + st));
                     bulk_load_1d(sVec(st) + kBlk * 4, p.delta + roff, kBlk * 4, BAR(B_QFULL + st));
-                    if (mk.mode == 1) {
-                        const int he = (mk.He == 1) ? 0 : h;
-                        const int32_t* qc = mk.plan + mk.L.off_qc + (int64_t(b) * mk.He + he) * mk.L.Mpad + int64_t(qb) * kBlk;
-                        bulk_load_1d(sVec(st) + 2 * kBlk * 4, qc, kBlk * 4, BAR(B_QFULL + st));
-                    }
                     if (use > 0) ok = mbar_wait(BAR(B_DOEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 42);
                     if (!ok) break;
                     mbar_expect_tx(BAR(B_DOFULL + st), S::TILE);
@@ -170,13 +207,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
         } else if (warp == 9 || warp == 10) {
             // ------------------------------ MMA issuers ------------------------------
-            // Two issuing threads, so that neither the blocking tcgen05.mma issue nor the barrier
-            // round trips of one pair of GEMMs delay the other pair:
-            //   warp 9 : dV(it) += P^T dO, then S^T(it+1) = K Q^T  (S^T overwrites P^T: same thread, in order)
-            //   warp 10: dK(it) += dS^T Q, then dP^T(it+1) = V dO^T (dP^T overwrites dS^T: same thread)
+            //   warp 9 : S^T(it) = K Q^T, as soon as the compute groups have read S^T(it-1)
+            //   warp 10: dV(it) += P^T dO when P^T is in shared memory, then dK(it) += dS^T Q and
+            //            dP^T(it+1) = V dO^T when dS^T is in TMEM (dP^T overwrites dS^T: same thread)
             // Each Q / dO stage is read by both threads, so its "empty" barrier takes two commits.
             if (lane == 0) {
-                const bool is_a = (warp == 9);
                 constexpr uint32_t idesc_s = make_idesc(BF16, 128, 128, false, false);
                 constexpr uint32_t idesc_d = make_idesc(BF16, 128, D, false, true);
                 constexpr uint64_t desc_mn = desc_mn_major(S::BOX);
@@ -191,42 +226,17 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 idesc_s, kk > 0);
                     }
                 };
-                auto acc_mmas = [&](int it, uint32_t a_base, uint32_t d, uint32_t b_tile) {
-#pragma unroll
-                    for (int kk = 0; kk < kBlk / 16; ++kk) {
-                        const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
-                        umma_ts(d, a_base + acol, smem_desc_at(desc_mn, b_tile + uint32_t(kk) * 2048u), idesc_d,
-                                (it > 0 || kk > 0) ? 1u : 0u);
-                    }
-                };
-                if (is_a) {
-                    if (ok) ok = q_ready(0);
-                    if (ok) {
-                        tc_fence_after();
-                        ss_mmas(tmem, sK, sQ(0));  // S^T(0)
-                        umma_commit(BAR(B_QEMPTY + 0));
-                        umma_commit(BAR(B_SFULL));
-                    }
+                if (warp == 9) {
                     for (int it = 0; it < NIT && ok; ++it) {
                         const int st = it % NST;
-                        const bool more = it + 1 < NIT;
-                        ok = do_ready(it);
-                        FA_TRACE_EV(2, 3);
-                        if (ok) ok = mbar_wait(BAR(B_PFULL), it & 1, ab, ST_WAIT_TIMEOUT + 46);
+                        ok = q_ready(it);
+                        // the S^T columns are free once every compute thread has loaded S^T(it-1)
+                        if (ok && it > 0) ok = mbar_wait(BAR(B_SFREE), (it - 1) & 1, ab, ST_WAIT_TIMEOUT + 46);
                         if (!ok) break;
                         tc_fence_after();
-                        FA_TRACE_EV(2, 4);
-                        acc_mmas(it, tmem, tmem + 256u, sdO(st));  // dV += P^T dO
-                        umma_commit(BAR(B_DOEMPTY + st));
-                        // Q(it+1) can only be loaded once dK(it-1) has released its stage, so it is
-                        // waited for here and not ahead of P(it)
-                        if (more) ok = q_ready(it + 1);
-                        if (ok && more) {
-                            tc_fence_after();
-                            ss_mmas(tmem, sK, sQ((it + 1) % NST));
-                            umma_commit(BAR(B_QEMPTY + (it + 1) % NST));
-                            umma_commit(BAR(B_SFULL));
-                        }
+                        ss_mmas(tmem, sK, sQ(st));
+                        umma_commit(BAR(B_QEMPTY + st));
+                        umma_commit(BAR(B_SFULL));
                         FA_TRACE_EV(2, 2);
                     }
                 } else {
@@ -234,30 +244,43 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     if (ok) {
                         tc_fence_after();
                         ss_mmas(tmem + 128u, sV, sdO(0));  // dP^T(0)
-                        umma_commit(BAR(B_DOEMPTY + 0));
                         umma_commit(BAR(B_DPFULL));
                     }
                     for (int it = 0; it < NIT && ok; ++it) {
                         const int st = it % NST;
                         const bool more = it + 1 < NIT;
-                        ok = q_ready(it);
-                        if (ok && more) ok = do_ready(it + 1);
-                        if (ok) ok = mbar_wait(BAR(B_DSFULL), it & 1, ab, ST_WAIT_TIMEOUT + 47);
-                        // S^T(it+1) gates the next P and must not share the tensor pipe with this
-                        // batch (the pipe serves both issuers in turn): let it finish first
-                        if (ok && more) ok = mbar_wait(BAR(B_SFULL), (it + 1) & 1, ab, ST_WAIT_TIMEOUT + 49);
+                        // dV(it) += P^T dO: A = P^T from shared memory (K-major), B = dO (MN-major)
+                        ok = mbar_wait(BAR(B_PFULL), it & 1, ab, ST_WAIT_TIMEOUT + 47);
                         if (!ok) break;
                         tc_fence_after();
-                        acc_mmas(it, tmem + 128u, tmem + 256u + uint32_t(D), sQ(st));  // dK += dS^T Q
+#pragma unroll
+                        for (int kk = 0; kk < kBlk / 16; ++kk) {
+                            const uint32_t off = uint32_t(kk >> 2) * S::BOX + uint32_t(kk & 3) * 32u;
+                            umma_ss(tmem + 256u, smem_desc_at(kDescKMajor, sP + off),
+                                    smem_desc_at(desc_mn, sdO(st) + uint32_t(kk) * 2048u), idesc_d, (it > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        umma_commit(BAR(B_PFREE));
+                        umma_commit(BAR(B_DOEMPTY + st));
+                        if (more) ok = do_ready(it + 1);
+                        if (ok) ok = mbar_wait(BAR(B_DSFULL), it & 1, ab, ST_WAIT_TIMEOUT + 48);
+                        if (!ok) break;
+                        tc_fence_after();
+                        // dK(it) += dS^T Q: A = dS^T from TMEM, B = Q (MN-major)
+#pragma unroll
+                        for (int kk = 0; kk < kBlk / 16; ++kk) {
+                            const uint32_t acol = (kk < 4) ? uint32_t(kk) * 8u : 64u + uint32_t(kk - 4) * 8u;
+                            umma_ts(tmem + 256u + uint32_t(D), tmem + 128u + acol,
+                                    smem_desc_at(desc_mn, sQ(st) + uint32_t(kk) * 2048u), idesc_d, (it > 0 || kk > 0) ? 1u : 0u);
+                        }
                         umma_commit(BAR(B_QEMPTY + st));
                         if (more) {
-                            ss_mmas(tmem + 128u, sV, sdO((it + 1) % NST));
-                            umma_commit(BAR(B_DOEMPTY + (it + 1) % NST));
+                            ss_mmas(tmem + 128u, sV, sdO((it + 1) % NST));  // dP^T(it+1)
                             umma_commit(BAR(B_DPFULL));
                         }
                     }
+                    if (ok) umma_commit(BAR(B_DONE));
                 }
-                if (ok) umma_commit(BAR(B_DONE));
+                if (warp == 9 && ok) umma_commit(BAR(B_DONE));
             }
         }
         __syncwarp();
@@ -274,77 +297,134 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t tS = tmem + lane_base + uint32_t(cbase);
         const uint32_t tdP = tmem + lane_base + 128u + uint32_t(cbase);
 
-        for (int it = 0; it < NIT && ok; ++it) {
-            const int g = it / T, idx = it - g * T;
-            const int he = (mk.He == 1) ? 0 : hk * G + g;
-            const uint32_t entry = list[idx];
-            const uint32_t fl = entry >> 10;
-            const int q0 = (lo + int(entry & 1023u)) * kBlk + cbase;  // first query row of this thread's columns
+        Cursor cur{0, first_from(0)};
+        int kc = 0, kc_g = -1;  // this key's code for the current query head
+        for (int it = 0; it < NIT && ok; ++it, advance(cur)) {
+            const int he = (mk.He == 1) ? 0 : hk * G + cur.g;
+            const uint32_t fl = flag_of(cur.c);
+            const int q0 = (lo + cur.c) * kBlk + cbase;  // first query row of this thread's columns
             const int st = it % NST;
             const float* vlse = reinterpret_cast<const float*>(smem + S::off_vec + st * S::VEC) + cbase;
             const float* vdelta = vlse + kBlk;
-            const int* vqc = reinterpret_cast<const int*>(vlse + 2 * kBlk);
 
             if (r == 0) FA_TRACE_EV(w, 10);
-            ok = mbar_wait(BAR(B_QFULL + st), (it / NST) & 1, ab, ST_WAIT_TIMEOUT + 48);
-            if (ok) ok = mbar_wait(BAR(B_SFULL), it & 1, ab, ST_WAIT_TIMEOUT + 49);
+            ok = mbar_wait(BAR(B_QFULL + st), (it / NST) & 1, ab, ST_WAIT_TIMEOUT + 49);
+            if (ok) ok = mbar_wait(BAR(B_SFULL), it & 1, ab, ST_WAIT_TIMEOUT + 50);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (r == 0) FA_TRACE_EV(w, 11);
             uint32_t sr[64];
             tmem_ld32(tS, sr);
             tmem_ld32(tS + 32u, sr + 32);
             tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(BAR(B_SFREE));  // S^T(it+1) may now overwrite the columns
             if (r == 0) FA_TRACE_EV(w, 12);
             float* pr = reinterpret_cast<float*>(sr);
             {
+                // P^T = exp2(S^T*c - LSE). MUFU bounds this phase, so on tiles without masked entries
+                // one pair in four goes through the FMA-pipe exp2 (whose result is never exactly 0,
+                // which masked entries need). A fully masked row has LSE = -inf and only occurs in
+                // flagged tiles.
                 const uint64_t c2 = pack_f2(c, c);
+                const bool poly_ok = (fl & (KF_RANGE | KF_DOC)) == 0;
 #pragma unroll
                 for (int q = 0; q < 16; ++q) {
                     const float4 l4 = *reinterpret_cast<const float4*>(vlse + 4 * q);
+                    const uint64_t xa = fma_f2(pack_f2(pr[4 * q + 0], pr[4 * q + 1]), c2, pack_f2(-l4.x, -l4.y));
+                    const uint64_t xb = fma_f2(pack_f2(pr[4 * q + 2], pr[4 * q + 3]), c2, pack_f2(-l4.z, -l4.w));
                     float x0, x1, x2, x3;
-                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 0], pr[4 * q + 1]), c2, pack_f2(-l4.x, -l4.y)), x0, x1);
-                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 2], pr[4 * q + 3]), c2, pack_f2(-l4.z, -l4.w)), x2, x3);
-                    pr[4 * q + 0] = fast_exp2(x0);
-                    pr[4 * q + 1] = fast_exp2(x1);
+                    unpack_f2(xb, x2, x3);
                     pr[4 * q + 2] = fast_exp2(x2);
                     pr[4 * q + 3] = fast_exp2(x3);
-                }
-            }
-            if (fl & (TILE_BOUND | TILE_DOC | TILE_QTAIL)) {
-                int cmin = -0x40000000, cmax = 64;  // keep iff cmin <= column < cmax
-                if ((fl & TILE_BOUND) && mk.causal) cmin = (j - mk.gap) - q0;
-                if (fl & TILE_QTAIL) cmax = mk.M - q0;
-                if (fl & TILE_DOC) {
-                    const int kc = mk.plan[mk.L.off_kc + (int64_t(b) * mk.He + he) * mk.L.Npad + j];
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) {
-                        const int4 qc = *reinterpret_cast<const int4*>(vqc + 4 * q);
-                        pr[4 * q + 0] = ((qc.x >= 0 || qc.x == kc) && 4 * q + 0 >= cmin && 4 * q + 0 < cmax) ? pr[4 * q + 0] : 0.f;
-                        pr[4 * q + 1] = ((qc.y >= 0 || qc.y == kc) && 4 * q + 1 >= cmin && 4 * q + 1 < cmax) ? pr[4 * q + 1] : 0.f;
-                        pr[4 * q + 2] = ((qc.z >= 0 || qc.z == kc) && 4 * q + 2 >= cmin && 4 * q + 2 < cmax) ? pr[4 * q + 2] : 0.f;
-                        pr[4 * q + 3] = ((qc.w >= 0 || qc.w == kc) && 4 * q + 3 >= cmin && 4 * q + 3 < cmax) ? pr[4 * q + 3] : 0.f;
+                    if (poly_ok && (q & 1) == 0) {
+                        exp2_poly2(xa, pr[4 * q + 0], pr[4 * q + 1]);
+                    } else {
+                        unpack_f2(xa, x0, x1);
+                        pr[4 * q + 0] = fast_exp2(x0);
+                        pr[4 * q + 1] = fast_exp2(x1);
                     }
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 64; ++x) pr[x] = (x >= cmin && x < cmax) ? pr[x] : 0.f;
                 }
             }
-            uint32_t pk[32];
+            if (fl & (KF_RANGE | KF_DOC)) {
+                // keep(x) = (cmin <= x < cmax) & (qc[x] >= 0 | qc[x] == kc), per 32-query chunk where
+                // the chunk lies on one side of the range and (monotone query codes) is one document
+                int cmin = -0x40000000, cmax = 64;
+                if (fl & KF_RANGE) {
+                    if (mk.causal) cmin = (j - mk.gap) - q0;
+                    cmax = min(64, mk.M - q0);
+                }
+                const int* qcs = nullptr;
+                if (fl & KF_DOC) {
+                    const int64_t bh_ids = int64_t(b) * mk.He + he;
+                    if (kc_g != cur.g) { kc = mk.plan[mk.L.off_kc + bh_ids * mk.L.Npad + j]; kc_g = cur.g; }
+                    qcs = mk.plan + mk.L.off_qc + bh_ids * mk.L.Mpad + q0;
+                }
 #pragma unroll
-            for (int x = 0; x < 32; ++x) pk[x] = pack2<BF16>(pr[2 * x], pr[2 * x + 1]);
-            tmem_st32(tS, pk);
-            tc_wait_st();
-            tc_fence_before();
+                for (int q = 0; q < 2; ++q) {
+                    int state = 0;  // this key in chunk q: 0 keep all, 1 mask all, 2 entry by entry
+                    if (32 * q >= cmax || 32 * q + 31 < cmin) state = 1;
+                    else if (32 * q < cmin || 32 * q + 31 >= cmax) state = 2;
+                    if ((fl & KF_DOC) && state != 1) {
+                        if (fl & KF_QMONO) {
+                            const int qf = __ldg(qcs + 32 * q), ql = __ldg(qcs + 32 * q + 31);
+                            if (qf != ql) state = 2;
+                            else if (!(qf >= 0 || qf == kc)) state = 1;
+                        } else {
+                            state = 2;
+                        }
+                    }
+                    if (!__any_sync(0xffffffffu, state == 2)) {
+                        if (state == 1) {
+#pragma unroll
+                            for (int x = 0; x < 32; ++x) pr[32 * q + x] = 0.f;
+                        }
+                    } else if (fl & KF_DOC) {
+                        const int4* qc4 = reinterpret_cast<const int4*>(qcs + 32 * q);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int4 qc = __ldg(qc4 + u);
+                            const int x = 32 * q + 4 * u;
+                            pr[x + 0] = ((qc.x >= 0 || qc.x == kc) && x + 0 >= cmin && x + 0 < cmax) ? pr[x + 0] : 0.f;
+                            pr[x + 1] = ((qc.y >= 0 || qc.y == kc) && x + 1 >= cmin && x + 1 < cmax) ? pr[x + 1] : 0.f;
+                            pr[x + 2] = ((qc.z >= 0 || qc.z == kc) && x + 2 >= cmin && x + 2 < cmax) ? pr[x + 2] : 0.f;
+                            pr[x + 3] = ((qc.w >= 0 || qc.w == kc) && x + 3 >= cmin && x + 3 < cmax) ? pr[x + 3] : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) pr[32 * q + x] = (32 * q + x >= cmin && 32 * q + x < cmax) ? pr[32 * q + x] : 0.f;
+                    }
+                }
+            }
+            // P^T (input dtype) -> shared memory, K-major 128-byte-swizzled rows: this thread's 64
+            // queries are one 128-byte row of box `w`. The previous tile's dV MMAs must have read it.
+            if (it > 0) {
+                ok = mbar_wait(BAR(B_PFREE), (it - 1) & 1, ab, ST_WAIT_TIMEOUT + 51);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            {
+                uint8_t* prow = smem + S::off_p + w * S::BOX + r * 128;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    uint4 v4;
+                    v4.x = pack2<BF16>(pr[8 * ch + 0], pr[8 * ch + 1]);
+                    v4.y = pack2<BF16>(pr[8 * ch + 2], pr[8 * ch + 3]);
+                    v4.z = pack2<BF16>(pr[8 * ch + 4], pr[8 * ch + 5]);
+                    v4.w = pack2<BF16>(pr[8 * ch + 6], pr[8 * ch + 7]);
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = v4;
+                }
+            }
+            fence_proxy_async();
             mbar_arrive(BAR(B_PFULL));
             if (r == 0) FA_TRACE_EV(w, 15);
 
-            ok = mbar_wait(BAR(B_DPFULL), it & 1, ab, ST_WAIT_TIMEOUT + 50);
+            ok = mbar_wait(BAR(B_DPFULL), it & 1, ab, ST_WAIT_TIMEOUT + 52);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             if (r == 0) FA_TRACE_EV(w, 16);
+            uint32_t pk[32];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t dp[32];
@@ -373,15 +453,17 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (ok && NIT > 0) ok = mbar_wait(BAR(B_DONE), 0, ab, ST_WAIT_TIMEOUT + 51);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        if (ok && misc[1] == 0) {
+        const bool healthy = ok && misc[1] == 0;
+        {
+            // dV and dK * sm_scale (flash_triton.py:313) go out through shared memory: each thread
+            // writes its half rows into the (now dead) V and K tiles in the tensor maps'
+            // 128-byte-swizzled layout, then one thread issues the TMA stores, which clip rows >= N.
             constexpr int HALF = D / 2;
             const uint32_t c0 = uint32_t(w) * HALF;
 #pragma unroll
             for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
-                const OutTensor& out = which ? p.dk : p.dv;
-                const float mul = which ? p.sm_scale : 1.0f;  // flash_triton.py:313
-                uint8_t* orow = static_cast<uint8_t*>(out.ptr) +
-                                2 * (int64_t(b) * out.sb + int64_t(hk) * out.sh + int64_t(j) * out.sl + c0);
+                const float mul = which ? p.sm_scale : 1.0f;
+                uint8_t* stage = smem + (which ? S::off_k : S::off_v);
 #pragma unroll
                 for (int q = 0; q < HALF / 32; ++q) {
                     uint32_t x[32];
@@ -394,12 +476,24 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         const float v1 = (NIT > 0) ? __uint_as_float(x[2 * y + 1]) * mul : 0.f;
                         o16[y] = pack2<BF16>(v0, v1);
                     }
-                    if (j < mk.N) {
-                        uint4* dst = reinterpret_cast<uint4*>(orow + q * 64);
 #pragma unroll
-                        for (int y = 0; y < 4; ++y) dst[y] = make_uint4(o16[4 * y], o16[4 * y + 1], o16[4 * y + 2], o16[4 * y + 3]);
+                    for (int i = 0; i < 4; ++i) {
+                        const int cg = int(c0) / 8 + 4 * q + i;  // 16-byte chunk of the row
+                        const int box = cg >> 3, ch = cg & 7;
+                        uint4* dst = reinterpret_cast<uint4*>(stage + box * S::BOX + r * 128 + ((ch ^ (r & 7)) << 4));
+                        *dst = make_uint4(o16[4 * i], o16[4 * i + 1], o16[4 * i + 2], o16[4 * i + 3]);
                     }
                 }
+            }
+            fence_proxy_async();
+            named_bar_sync(1, 256);
+            if (tid == 0 && healthy) {
+                for (int x = 0; x < S::NBOX; ++x) {
+                    tma_store_4d(&tmdV, sbase + S::off_v + x * S::BOX, x * 64, kb * kBlk, hk, b);
+                    tma_store_4d(&tmdK, sbase + S::off_k + x * S::BOX, x * 64, kb * kBlk, hk, b);
+                }
+                tma_store_commit();
+                tma_store_wait_all();
             }
         }
     }
@@ -414,24 +508,26 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 template <int D, bool BF16>
 static cudaError_t launch_dkdv_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                 const CUtensorMap& tdo, const DkdvParams& p, int B, cudaStream_t stream) {
+                                 const CUtensorMap& tdo, const CUtensorMap& tdk, const CUtensorMap& tdv,
+                                 const DkdvParams& p, int B, cudaStream_t stream) {
     auto kern = bwd_dkdv_kernel<D, BF16>;
     constexpr int smem = DkdvSmem<D>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     dim3 grid(p.mask.L.nK, p.Hk, B);
-    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, p);
+    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, tdk, tdv, p);
     return cudaGetLastError();
 }
 
 FA_TRACE_DUMP_FN(fa_trace_dump_dkdv)
 
 cudaError_t launch_bwd_dkdv(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                            const CUtensorMap& tdo, const DkdvParams& p, int B, cudaStream_t stream) {
-    if (D == 128) return bf16 ? launch_dkdv_t<128, true>(tq, tk, tv, tdo, p, B, stream)
-                              : launch_dkdv_t<128, false>(tq, tk, tv, tdo, p, B, stream);
-    return bf16 ? launch_dkdv_t<64, true>(tq, tk, tv, tdo, p, B, stream)
-                : launch_dkdv_t<64, false>(tq, tk, tv, tdo, p, B, stream);
+                            const CUtensorMap& tdo, const CUtensorMap& tdk, const CUtensorMap& tdv,
+                            const DkdvParams& p, int B, cudaStream_t stream) {
+    if (D == 128) return bf16 ? launch_dkdv_t<128, true>(tq, tk, tv, tdo, tdk, tdv, p, B, stream)
+                              : launch_dkdv_t<128, false>(tq, tk, tv, tdo, tdk, tdv, p, B, stream);
+    return bf16 ? launch_dkdv_t<64, true>(tq, tk, tv, tdo, tdk, tdv, p, B, stream)
+                : launch_dkdv_t<64, false>(tq, tk, tv, tdo, tdk, tdv, p, B, stream);
 }
 
 }  // namespace fa

@@ -37,7 +37,8 @@ struct DqSmem {
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const DqParams p) {
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+              const __grid_constant__ CUtensorMap tmdQ, const DqParams p) {
     using S = DqSmem<D>;
     constexpr int NSK = S::NSK, NSV = S::NSV;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -238,13 +239,32 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             float* pr = reinterpret_cast<float*>(sr);
             if (r == 0) FA_TRACE_EV(w, 12);
             {
+                // P = exp2(S*c - LSE). MUFU (16 ex2 per clock and SM) bounds this phase, so on tiles
+                // without masked entries one pair in four goes through the FMA-pipe exp2 instead
+                // (its result is never exactly 0, which masked entries need).
                 const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(-lse, -lse);
+                const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
+                if (poly_ok) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x0, x1;
-                    unpack_f2(fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2), x0, x1);
-                    pr[2 * j] = fast_exp2(x0);
-                    pr[2 * j + 1] = fast_exp2(x1);
+                    for (int j = 0; j < 32; ++j) {
+                        const uint64_t x2 = fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2);
+                        if ((j & 3) == 0) {
+                            exp2_poly2(x2, pr[2 * j], pr[2 * j + 1]);
+                        } else {
+                            float x0, x1;
+                            unpack_f2(x2, x0, x1);
+                            pr[2 * j] = fast_exp2(x0);
+                            pr[2 * j + 1] = fast_exp2(x1);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x0, x1;
+                        unpack_f2(fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2), x0, x1);
+                        pr[2 * j] = fast_exp2(x0);
+                        pr[2 * j + 1] = fast_exp2(x1);
+                    }
                 }
             }
             if (fl & (TILE_BOUND | TILE_DOC)) {
@@ -304,11 +324,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (ok && T > 0) ok = mbar_wait(BAR(B_DONE), 0, ab, ST_WAIT_TIMEOUT + 29);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        if (ok && misc[1] == 0) {
+        const bool healthy = ok && misc[1] == 0;
+        {
+            // dQ * sm_scale (flash_triton.py:425) goes out through shared memory: each thread writes
+            // its half row into the (now dead) Q tile in the tensor map's 128-byte-swizzled layout,
+            // then one thread issues the TMA store, which clips rows >= M.
             constexpr int HALF = D / 2;
             const uint32_t c0 = uint32_t(w) * HALF;
-            uint8_t* orow = static_cast<uint8_t*>(p.dq.ptr) +
-                            2 * (int64_t(b) * p.dq.sb + int64_t(h) * p.dq.sh + int64_t(row) * p.dq.sl + c0);
+            uint8_t* stage = smem + S::off_q;
 #pragma unroll
             for (int q = 0; q < HALF / 32; ++q) {
                 uint32_t x[32];
@@ -321,11 +344,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     const float v1 = (T > 0) ? __uint_as_float(x[2 * j + 1]) * p.sm_scale : 0.f;
                     out[j] = pack2<BF16>(v0, v1);
                 }
-                if (row < mk.M) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + q * 64);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                for (int i = 0; i < 4; ++i) {
+                    const int cg = int(c0) / 8 + 4 * q + i;  // 16-byte chunk of the row
+                    const int box = cg >> 3, ch = cg & 7;
+                    uint4* dst = reinterpret_cast<uint4*>(stage + box * S::BOX + r * 128 + ((ch ^ (r & 7)) << 4));
+                    *dst = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
                 }
+            }
+            fence_proxy_async();
+            named_bar_sync(1, 256);
+            if (tid == 0 && healthy) {
+                for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmdQ, sbase + S::off_q + x * S::BOX, x * 64, qb * kBlk, h, b);
+                tma_store_commit();
+                tma_store_wait_all();
             }
         }
     }
@@ -340,24 +372,25 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
 template <int D, bool BF16>
 static cudaError_t launch_dq_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const CUtensorMap& tdo, const DqParams& p, int B, cudaStream_t stream) {
+                               const CUtensorMap& tdo, const CUtensorMap& tdq, const DqParams& p, int B,
+                               cudaStream_t stream) {
     auto kern = bwd_dq_kernel<D, BF16>;
     constexpr int smem = DqSmem<D>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     dim3 grid(p.mask.L.nQ, p.H, B);
-    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, p);
+    kern<<<grid, kAttnThreads, smem, stream>>>(tq, tk, tv, tdo, tdq, p);
     return cudaGetLastError();
 }
 
 FA_TRACE_DUMP_FN(fa_trace_dump_dq)
 
 cudaError_t launch_bwd_dq(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                          const CUtensorMap& tdo, const DqParams& p, int B, cudaStream_t stream) {
-    if (D == 128) return bf16 ? launch_dq_t<128, true>(tq, tk, tv, tdo, p, B, stream)
-                              : launch_dq_t<128, false>(tq, tk, tv, tdo, p, B, stream);
-    return bf16 ? launch_dq_t<64, true>(tq, tk, tv, tdo, p, B, stream)
-                : launch_dq_t<64, false>(tq, tk, tv, tdo, p, B, stream);
+                          const CUtensorMap& tdo, const CUtensorMap& tdq, const DqParams& p, int B, cudaStream_t stream) {
+    if (D == 128) return bf16 ? launch_dq_t<128, true>(tq, tk, tv, tdo, tdq, p, B, stream)
+                              : launch_dq_t<128, false>(tq, tk, tv, tdo, tdq, p, B, stream);
+    return bf16 ? launch_dq_t<64, true>(tq, tk, tv, tdo, tdq, p, B, stream)
+                : launch_dq_t<64, false>(tq, tk, tv, tdo, tdq, p, B, stream);
 }
 
 }  // namespace fa

@@ -25,7 +25,6 @@ struct DeltaParams {
 };
 
 struct DkdvParams {
-    OutTensor dk, dv;    // [B, Hk, N, D]
     const float* lse;    // [B, H, Mpad]
     const float* delta;  // [B, H, Mpad]
     MaskArgs mask;
@@ -35,7 +34,6 @@ struct DkdvParams {
 };
 
 struct DqParams {
-    OutTensor dq;        // [B, H, M, D]
     const float* lse;
     const float* delta;
     MaskArgs mask;
