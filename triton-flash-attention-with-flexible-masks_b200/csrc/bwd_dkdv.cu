@@ -74,6 +74,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     FA_TRACE_DECL
+    if (tid == 0) FA_TRACE_EV(0, 40);
 
     const MaskArgs& mk = p.mask;
     const int kb = blockIdx.x;  // with a causal mask the first key blocks are the long ones
@@ -89,21 +90,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               B_PFREE = B_SFULL + 4, B_DSFULL = B_SFULL + 5, B_DONE = B_SFULL + 6;
     Abort ab{misc + 1, p.status};
 
-    // union of the query-block ranges of the group's heads
-    int lo = 0x7fffffff, hi = 0;
-    {
-        const int ng = (mk.He == 1) ? 1 : G;
-        for (int g = 0; g < ng; ++g) {
-            int l, h2;
-            q_range(mk, b, mk.He == 1 ? 0 : hk * G + g, kb, l, h2);
-            if (h2 > l) { lo = min(lo, l); hi = max(hi, h2); }
-        }
-        if (hi == 0) lo = 0;
-    }
-    int n = hi - lo;
-    if (n > kListCap) n = kListCap;
+    const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v, sP = sbase + S::off_p;
+    auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
+    auto sdO = [&](int s) { return sbase + S::off_do + uint32_t(s) * S::TILE; };
+    auto sVec = [&](int s) { return sbase + S::off_vec + uint32_t(s) * S::VEC; };
 
-    if (tid == 0) {
+    // The producer thread sets up the barriers itself, so that it can start the K / V loads (which
+    // do not depend on the plan) before anything else happens in the CTA.
+    const bool producer = (warp == 8 && lane == 0);
+    if (producer) {
         mbar_init(BAR(B_KV), 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(BAR(B_QFULL + s), 1); mbar_init(BAR(B_DOFULL + s), 1);
@@ -120,10 +115,51 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
         misc[2] = 0;
         fence_mbar_init();
+        if (misc[1] == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            mbar_expect_tx(BAR(B_KV), 2 * S::TILE);
+            for (int x = 0; x < S::NBOX; ++x) {
+                tma_load_4d(sK + x * S::BOX, &tmK, BAR(B_KV), x * 64, kb * kBlk, hk, b);
+                tma_load_4d(sV + x * S::BOX, &tmV, BAR(B_KV), x * 64, kb * kBlk, hk, b);
+            }
+        }
     }
     if (warp == 9) {
         tmem_alloc(sbase + S::off_misc, 512);
         tmem_relinquish();
+    }
+
+    // union of the query-block ranges of the group's heads
+    int lo = 0x7fffffff, hi = 0;
+    {
+        const int ng = (mk.He == 1) ? 1 : G;
+        for (int g = 0; g < ng; ++g) {
+            int l, h2;
+            q_range(mk, b, mk.He == 1 ? 0 : hk * G + g, kb, l, h2);
+            if (h2 > l) { lo = min(lo, l); hi = max(hi, h2); }
+        }
+        if (hi == 0) lo = 0;
+    }
+    int n = hi - lo;
+    if (n > kListCap) n = kListCap;
+
+    // ... and the first visited query block's Q / dO / LSE / delta as soon as it knows which block
+    // that is (normally candidate 0: the range starts at a visited block)
+    if (producer && misc[1] == 0) {
+        int c0 = 0;
+        while (c0 < n && !(classify_group(mk, b, hk, G, lo + c0, kb) & TILE_VISIT)) ++c0;
+        if (c0 < n) {
+            const int h = hk * G, qb = lo + c0;
+            mbar_expect_tx(BAR(B_QFULL + 0), S::TILE + S::VEC);
+            mbar_expect_tx(BAR(B_DOFULL + 0), S::TILE);
+            for (int x = 0; x < S::NBOX; ++x) {
+                tma_load_4d(sQ(0) + x * S::BOX, &tmQ, BAR(B_QFULL + 0), x * 64, qb * kBlk, h, b);
+                tma_load_4d(sdO(0) + x * S::BOX, &tmdO, BAR(B_DOFULL + 0), x * 64, qb * kBlk, h, b);
+            }
+            const int64_t roff = (int64_t(b) * p.H + h) * mk.L.Mpad + int64_t(qb) * kBlk;
+            bulk_load_1d(sVec(0), p.lse + roff, kBlk * 4, BAR(B_QFULL + 0));
+            bulk_load_1d(sVec(0) + kBlk * 4, p.delta + roff, kBlk * 4, BAR(B_QFULL + 0));
+        }
     }
     // flags of the candidate query blocks [lo, lo+n), two per byte
     for (int i = tid; 2 * i < n; i += kAttnThreads) {
@@ -143,9 +179,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         flags[i] = uint8_t(byte);
     }
+    if (tid == 0) FA_TRACE_EV(0, 41);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (tid == 0) FA_TRACE_EV(0, 42);
     if (warp == 0) {  // number of visited candidates
         int cnt = 0;
         for (int i = lane; 2 * i < n; i += 32) cnt += (flags[i] & KF_VISIT) + ((flags[i] >> 4) & KF_VISIT);
@@ -153,6 +191,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (lane == 0) misc[2] = cnt;
     }
     __syncthreads();
+    if (tid == 0) FA_TRACE_EV(0, 43);
     const uint32_t tmem = uint32_t(misc[0]);
     const int T = misc[2];
     const int NIT = T * G;  // tiles of all query heads of the group, head-major
@@ -167,26 +206,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (cur.c >= n) { cur.g += 1; cur.c = first_from(0); }
     };
 
-    const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v, sP = sbase + S::off_p;
-    auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
-    auto sdO = [&](int s) { return sbase + S::off_do + uint32_t(s) * S::TILE; };
-    auto sVec = [&](int s) { return sbase + S::off_vec + uint32_t(s) * S::VEC; };
-
     if (warp >= 8) {
         setmaxnreg_dec<56>();
         if (aborted || NIT == 0) {
         } else if (warp == 8) {
             // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
-                tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-                mbar_expect_tx(BAR(B_KV), 2 * S::TILE);
-                for (int x = 0; x < S::NBOX; ++x) {
-                    tma_load_4d(sK + x * S::BOX, &tmK, BAR(B_KV), x * 64, kb * kBlk, hk, b);
-                    tma_load_4d(sV + x * S::BOX, &tmV, BAR(B_KV), x * 64, kb * kBlk, hk, b);
-                }
                 bool ok = true;
                 Cursor cur{0, first_from(0)};
-                for (int it = 0; it < NIT && ok; ++it, advance(cur)) {
+                advance(cur);  // tile 0 is already under way
+                for (int it = 1; it < NIT && ok; ++it, advance(cur)) {
                     const int h = hk * G + cur.g;
                     const int qb = lo + cur.c;
                     const int st = it % NST, use = it / NST;
@@ -322,28 +351,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (r == 0) FA_TRACE_EV(w, 12);
             float* pr = reinterpret_cast<float*>(sr);
             {
-                // P^T = exp2(S^T*c - LSE). MUFU bounds this phase, so on tiles without masked entries
-                // one pair in four goes through the FMA-pipe exp2 (whose result is never exactly 0,
-                // which masked entries need). A fully masked row has LSE = -inf and only occurs in
-                // flagged tiles.
+                // P^T = exp2(S^T*c - LSE) on packed pairs. A fully masked row has LSE = -inf and only
+                // occurs in flagged tiles.
                 const uint64_t c2 = pack_f2(c, c);
-                const bool poly_ok = (fl & (KF_RANGE | KF_DOC)) == 0;
 #pragma unroll
                 for (int q = 0; q < 16; ++q) {
                     const float4 l4 = *reinterpret_cast<const float4*>(vlse + 4 * q);
-                    const uint64_t xa = fma_f2(pack_f2(pr[4 * q + 0], pr[4 * q + 1]), c2, pack_f2(-l4.x, -l4.y));
-                    const uint64_t xb = fma_f2(pack_f2(pr[4 * q + 2], pr[4 * q + 3]), c2, pack_f2(-l4.z, -l4.w));
                     float x0, x1, x2, x3;
-                    unpack_f2(xb, x2, x3);
+                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 0], pr[4 * q + 1]), c2, pack_f2(-l4.x, -l4.y)), x0, x1);
+                    unpack_f2(fma_f2(pack_f2(pr[4 * q + 2], pr[4 * q + 3]), c2, pack_f2(-l4.z, -l4.w)), x2, x3);
+                    pr[4 * q + 0] = fast_exp2(x0);
+                    pr[4 * q + 1] = fast_exp2(x1);
                     pr[4 * q + 2] = fast_exp2(x2);
                     pr[4 * q + 3] = fast_exp2(x3);
-                    if (poly_ok && (q & 1) == 0) {
-                        exp2_poly2(xa, pr[4 * q + 0], pr[4 * q + 1]);
-                    } else {
-                        unpack_f2(xa, x0, x1);
-                        pr[4 * q + 0] = fast_exp2(x0);
-                        pr[4 * q + 1] = fast_exp2(x1);
-                    }
                 }
             }
             if (fl & (KF_RANGE | KF_DOC)) {
@@ -451,8 +471,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
         // ------------------------------ epilogue ------------------------------
         if (ok && NIT > 0) ok = mbar_wait(BAR(B_DONE), 0, ab, ST_WAIT_TIMEOUT + 51);
+        // without visited tiles nobody has waited for the K / V loads yet, and their tiles are the staging area
+        if (ok && NIT == 0) ok = mbar_wait(BAR(B_KV), 0, ab, ST_WAIT_TIMEOUT + 53);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
+        if (r == 0) FA_TRACE_EV(w, 44);
         const bool healthy = ok && misc[1] == 0;
         {
             // dV and dK * sm_scale (flash_triton.py:313) go out through shared memory: each thread
@@ -487,19 +510,22 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             fence_proxy_async();
             named_bar_sync(1, 256);
+            if (r == 0) FA_TRACE_EV(w, 45);
             if (tid == 0 && healthy) {
                 for (int x = 0; x < S::NBOX; ++x) {
                     tma_store_4d(&tmdV, sbase + S::off_v + x * S::BOX, x * 64, kb * kBlk, hk, b);
                     tma_store_4d(&tmdK, sbase + S::off_k + x * S::BOX, x * 64, kb * kBlk, hk, b);
                 }
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read();
             }
+            if (r == 0) FA_TRACE_EV(w, 46);
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) FA_TRACE_EV(0, 47);
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);

@@ -60,12 +60,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               B_SFULL = B_VEMPTY + NSV, B_DSFULL = B_SFULL + 2, B_DPFULL = B_DSFULL + 2, B_DONE = B_DPFULL + 1;
     Abort ab{misc + 1, p.status};
 
-    int lo, hi;
-    kv_range(mk, b, he, qb, lo, hi);
-    int n = hi - lo;
-    if (n > kListCap) n = kListCap;
+    const uint32_t sQ = sbase + S::off_q, sdO = sbase + S::off_do;
+    auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };
+    auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
 
-    if (tid == 0) {
+    // The producer thread sets up the barriers itself, so that it can start the Q / dO loads (which
+    // do not depend on the plan) before anything else happens in the CTA.
+    const bool producer = (warp == 8 && lane == 0);
+    if (producer) {
         mbar_init(BAR(B_QDO), 1);
         for (int s = 0; s < NSK; ++s) { mbar_init(BAR(B_KFULL + s), 1); mbar_init(BAR(B_KEMPTY + s), 1); }
         for (int s = 0; s < NSV; ++s) { mbar_init(BAR(B_VFULL + s), 1); mbar_init(BAR(B_VEMPTY + s), 1); }
@@ -75,10 +77,36 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
         misc[2] = 0;
         fence_mbar_init();
+        if (misc[1] == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            mbar_expect_tx(BAR(B_QDO), 2 * S::TILE);
+            for (int x = 0; x < S::NBOX; ++x) {
+                tma_load_4d(sQ + x * S::BOX, &tmQ, BAR(B_QDO), x * 64, qb * kBlk, h, b);
+                tma_load_4d(sdO + x * S::BOX, &tmdO, BAR(B_QDO), x * 64, qb * kBlk, h, b);
+            }
+        }
     }
     if (warp == 9) {
         tmem_alloc(sbase + S::off_misc, 512);
         tmem_relinquish();
+    }
+    int lo, hi;
+    kv_range(mk, b, he, qb, lo, hi);
+    int n = hi - lo;
+    if (n > kListCap) n = kListCap;
+    // ... and the first visited key block's K and V as soon as it knows which block that is
+    // (normally candidate 0: the range starts at a visited block)
+    if (producer && misc[1] == 0) {
+        int c0 = 0;
+        while (c0 < n && !(classify_from_plan(mk, b, he, qb, lo + c0) & TILE_VISIT)) ++c0;
+        if (c0 < n) {
+            mbar_expect_tx(BAR(B_KFULL + 0), S::TILE);
+            mbar_expect_tx(BAR(B_VFULL + 0), S::TILE);
+            for (int x = 0; x < S::NBOX; ++x) {
+                tma_load_4d(sK(0) + x * S::BOX, &tmK, BAR(B_KFULL + 0), x * 64, (lo + c0) * kBlk, hk, b);
+                tma_load_4d(sV(0) + x * S::BOX, &tmV, BAR(B_VFULL + 0), x * 64, (lo + c0) * kBlk, hk, b);
+            }
+        }
     }
     for (int i = tid; i < n; i += kAttnThreads) list[i] = uint16_t(classify_from_plan(mk, b, he, qb, lo + i));
     tc_fence_before();
@@ -93,25 +121,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int T = misc[2];
     const bool aborted = misc[1] != 0;
 
-    const uint32_t sQ = sbase + S::off_q, sdO = sbase + S::off_do;
-    auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };
-    auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
-
     if (warp >= 8) {
         setmaxnreg_dec<56>();
         if (aborted || T == 0) {
         } else if (warp == 8) {
             // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
-                tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-                mbar_expect_tx(BAR(B_QDO), 2 * S::TILE);
-                for (int x = 0; x < S::NBOX; ++x) {
-                    tma_load_4d(sQ + x * S::BOX, &tmQ, BAR(B_QDO), x * 64, qb * kBlk, h, b);
-                    tma_load_4d(sdO + x * S::BOX, &tmdO, BAR(B_QDO), x * 64, qb * kBlk, h, b);
-                }
                 bool ok = true;
-                for (int t = 0; t <= T && ok; ++t) {  // K runs one tile ahead of V
-                    if (t < T) {
+                for (int t = 0; t <= T && ok; ++t) {  // K runs one tile ahead of V; K(0), V(0) are already under way
+                    if (t < T && t > 0) {
                         const int kb = lo + (list[t] & 1023);
                         const int st = t % NSK, use = t / NSK;
                         if (use > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 21);
@@ -120,7 +138,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         for (int x = 0; x < S::NBOX; ++x)
                             tma_load_4d(sK(st) + x * S::BOX, &tmK, BAR(B_KFULL + st), x * 64, kb * kBlk, hk, b);
                     }
-                    if (t >= 1) {
+                    if (t >= 2) {
                         const int tv = t - 1;
                         const int kb = lo + (list[tv] & 1023);
                         const int st = tv % NSV, use = tv / NSV;
@@ -239,32 +257,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             float* pr = reinterpret_cast<float*>(sr);
             if (r == 0) FA_TRACE_EV(w, 12);
             {
-                // P = exp2(S*c - LSE). MUFU (16 ex2 per clock and SM) bounds this phase, so on tiles
-                // without masked entries one pair in four goes through the FMA-pipe exp2 instead
-                // (its result is never exactly 0, which masked entries need).
+                // P = exp2(S*c - LSE) on packed pairs
                 const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(-lse, -lse);
-                const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
-                if (poly_ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint64_t x2 = fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2);
-                        if ((j & 3) == 0) {
-                            exp2_poly2(x2, pr[2 * j], pr[2 * j + 1]);
-                        } else {
-                            float x0, x1;
-                            unpack_f2(x2, x0, x1);
-                            pr[2 * j] = fast_exp2(x0);
-                            pr[2 * j + 1] = fast_exp2(x1);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x0, x1;
-                        unpack_f2(fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2), x0, x1);
-                        pr[2 * j] = fast_exp2(x0);
-                        pr[2 * j + 1] = fast_exp2(x1);
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    float x0, x1;
+                    unpack_f2(fma_f2(pack_f2(pr[2 * j], pr[2 * j + 1]), c2, nl2), x0, x1);
+                    pr[2 * j] = fast_exp2(x0);
+                    pr[2 * j + 1] = fast_exp2(x1);
                 }
             }
             if (fl & (TILE_BOUND | TILE_DOC)) {
@@ -322,6 +322,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
         // ------------------------------ epilogue ------------------------------
         if (ok && T > 0) ok = mbar_wait(BAR(B_DONE), 0, ab, ST_WAIT_TIMEOUT + 29);
+        // without visited tiles nobody has waited for the Q / dO loads yet, and Q's tile is the staging area
+        if (ok && T == 0) ok = mbar_wait(BAR(B_QDO), 0, ab, ST_WAIT_TIMEOUT + 30);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         const bool healthy = ok && misc[1] == 0;
@@ -357,7 +359,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (tid == 0 && healthy) {
                 for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmdQ, sbase + S::off_q + x * S::BOX, x * 64, qb * kBlk, h, b);
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read();
             }
         }
     }

@@ -28,7 +28,6 @@
 
 namespace fa {
 
-constexpr int kPolyOf4 = 1;  // of every 4 pairs of scores, how many take the FMA-pipe exp2
 constexpr int kTurnMinTiles = 8;  // items with fewer visited tiles do not serialise their exp phases
 
 template <int D>
@@ -206,6 +205,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                             const int g = G + t, st = g % NS, ug = g / NS;
                             if (ug > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 1);
                             if (!ok) break;
+                            FA_TRACE_EV(4, 30);
                             // The tile's key codes are fetched with K into a ring of NKC slots (own barriers). Slot g % NKC was
                             // last read by the softmax of tile g - NKC, which is over: this thread has
                             // already waited for the P*V of tile g - 2 - NS before issuing V(g - 2).
@@ -224,6 +224,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                             const int g = G + t - 1, st = g % NS, ug = g / NS;
                             if (ug > 0) ok = mbar_wait(BAR(B_VEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 2);
                             if (!ok) break;
+                            FA_TRACE_EV(4, 31);
                             mbar_expect_tx(BAR(B_VFULL + st), S::TILE);
                             for (int x = 0; x < S::NBOX; ++x)
                                 tma_load_4d(sV(st) + x * S::BOX, &tmV, BAR(B_VFULL + st), x * 64, kb * kBlk, hk, b);
@@ -287,25 +288,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         const int g = G + w + 2 * i, st = g % NS;
                         const bool more = i + 1 < nmine;
                         ok = mbar_wait(BAR(B_VFULL + st), (g / NS) & 1, ab, ST_WAIT_TIMEOUT + 5);
+                        FA_TRACE_EV(2 + w, 20);
                         if (ok && more) ok = k_ready(g + 2);
+                        FA_TRACE_EV(2 + w, 21);
                         // the first P*V of an item overwrites O: the previous item's epilogue must have read it
                         if (ok && i == 0 && k > 0) ok = mbar_wait(BAR(B_OFREE + w), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 14);
                         if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
                         if (!ok) break;
                         tc_fence_after();
+                        FA_TRACE_EV(2 + w, 22);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk)
                             umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv,
                                     (i > 0 || kk > 0) ? 1u : 0u);
+                        FA_TRACE_EV(2 + w, 23);
                         ok = mbar_wait(BAR(B_PHALF1 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
                         if (!ok) break;
                         tc_fence_after();
+                        FA_TRACE_EV(2 + w, 24);
 #pragma unroll
                         for (int kk = 4; kk < 8; ++kk)
                             umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv, 1u);
                         umma_commit(BAR(B_VEMPTY + st));
                         umma_commit(BAR(B_PVDONE + w));
                         if (more) s_mmas(g + 2);
+                        FA_TRACE_EV(2 + w, 25);
                     }
                     G += T;
                     if (ok) mbar_arrive(BAR(B_ITEMEMPTY + s));
@@ -357,13 +364,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 tc_fence_after();
-                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 5);
+                if (r == 0) FA_TRACE_EV(w, 5);
                 uint32_t sr[128];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + uint32_t(q) * 32u, sr + q * 32);
                 tc_wait_ld();
                 float* sc = reinterpret_cast<float*>(sr);
-                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 6);
+                if (r == 0) FA_TRACE_EV(w, 6);
 
                 if (fl & (TILE_BOUND | TILE_DOC)) {
                     // keep(x) = (x <= lim) & (qc >= 0 | kc[x] == qc). The compare + select per entry is
@@ -384,7 +391,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         alive = __all_sync(0xffffffffu, alive);
                         if (!alive) break;
                     }
-                    if (r == 0 && n_my == 0) FA_TRACE_EV(w, 11);
+                    if (r == 0) FA_TRACE_EV(w, 11);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         int state = 0;  // this row in chunk q: 0 keep all, 1 mask all, 2 entry by entry
@@ -421,7 +428,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         }
                     }
                 }
-                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 7);
+                if (r == 0) FA_TRACE_EV(w, 7);
                 float mxa[8];
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mxa[a] = max3(sc[a], sc[8 + a], sc[16 + a]);
@@ -457,13 +464,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         tc_wait_st();
                     }
                 }
-                if (r == 0 && n_my == 0) FA_TRACE_EV(w, 8);
+                if (r == 0) FA_TRACE_EV(w, 8);
                 m_run = m_new;
                 const float mneg = (m_run == -INFINITY) ? 0.f : -m_run * c;
                 // exp2(s*c - m*c) on packed pairs; P goes to TMEM in two halves so that the first four
-                // k-steps of P*V can start while the second half is still being exponentiated. MUFU
-                // (16 ex2 per clock and SM) is as scarce as the tensor pipe here, so on tiles without
-                // masked entries kPolyOf4 of every 4 pairs are evaluated on the FMA pipe instead.
+                // k-steps of P*V can start while the second half is still being exponentiated.
                 const uint64_t c2 = pack_f2(c, c), mneg2 = pack_f2(mneg, mneg);
                 uint64_t lacc0 = pack_f2(0.f, 0.f), lacc1 = lacc0;
                 // The exp phase is taken in turns (barriers turn[0], turn[1]; group 0 first): left alone,
@@ -476,23 +481,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     if (!alive) break;
                     ++nturn;
                 }
-                const bool poly_ok = (fl & (TILE_BOUND | TILE_DOC)) == 0;
-                auto exp_half = [&](auto use_poly, int half) {
+                auto exp_half = [&](int half) {
 #pragma unroll
                     for (int q = 2 * half; q < 2 * half + 2; ++q) {
                         uint32_t pk[16];
 #pragma unroll
                         for (int x = 0; x < 16; ++x) {
                             const uint64_t x2 = fma_f2(pack_f2(sc[32 * q + 2 * x], sc[32 * q + 2 * x + 1]), c2, mneg2);
-                            float p0, p1;
-                            if (decltype(use_poly)::value && (x & 3) < kPolyOf4) {
-                                exp2_poly2(x2, p0, p1);
-                            } else {
-                                float x0, x1;
-                                unpack_f2(x2, x0, x1);
-                                p0 = fast_exp2(x0);
-                                p1 = fast_exp2(x1);
-                            }
+                            float x0, x1;
+                            unpack_f2(x2, x0, x1);
+                            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                             if (x & 1) lacc1 = add_f2(lacc1, pack_f2(p0, p1)); else lacc0 = add_f2(lacc0, pack_f2(p0, p1));
                             pk[x] = pack2<BF16>(p0, p1);
                         }
@@ -501,15 +499,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(BAR((half ? B_PHALF1 : B_PHALF0) + w));
-                    if (r == 0 && n_my == 0) FA_TRACE_EV(w, 9 + half);
+                    if (r == 0) FA_TRACE_EV(w, 9 + half);
                 };
-                if (poly_ok) {
-                    exp_half(std::true_type{}, 0);
-                    exp_half(std::true_type{}, 1);
-                } else {
-                    exp_half(std::false_type{}, 0);
-                    exp_half(std::false_type{}, 1);
-                }
+                exp_half(0);
+                exp_half(1);
                 // hand the turn over, unless the other group has no tile left to take it for
                 if (turns && (w == 0 ? (n_my < n_other) : (n_my + 1 < n_other))) mbar_arrive(BAR(B_TURN + (w ^ 1)));
                 {
