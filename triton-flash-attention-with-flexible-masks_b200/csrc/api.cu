@@ -246,14 +246,17 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     if ((rc = make_map(&tdv, dv, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     kp.lse = lse;
     kp.delta = delta;
+    kp.B = p->B;
     kp.H = p->H;
     kp.Hk = p->Hk;
     kp.G = p->H / p->Hk;
     kp.scale_log2 = p->sm_scale * kLog2e;
     kp.sm_scale = p->sm_scale;
     kp.status = status;
+    const int sms = sm_count();
+    if (sms <= 0) return FA_ERR_LAUNCH;
     const cudaError_t e =
-        fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdk, tdv, kp, p->B,
+        fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdk, tdv, kp, sms,
                             static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
 }

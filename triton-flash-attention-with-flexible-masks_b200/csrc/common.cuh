@@ -27,10 +27,13 @@ __host__ __device__ inline int64_t pad128(int64_t x) { return (x + 127) / 128 * 
 //   q_lo, q_hi   [B, He, nK] range of query blocks with an unmasked entry, per key block
 //   qmono [B, He, nQ], kmono [B, He, nK]  1 if the codes of the block are monotone (non-decreasing or
 //                non-increasing), i.e. equal codes are adjacent: the usual packed-documents layout
+//   ctr [128]    work counters of the persistent kernels (item counter, finished-CTA counter per kernel);
+//                zero between launches: the plan build clears them and every kernel clears its pair
+//                when its last CTA leaves, so a plan serves one launch of each kernel at a time
 struct PlanLayout {
     int B, He, M, N, nQ, nK;
     int64_t Mpad, Npad;
-    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi, off_qmono, off_kmono;
+    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi, off_qmono, off_kmono, off_ctr;
     int64_t total;  // int32 elements
 
     __host__ __device__ PlanLayout() {}
@@ -52,6 +55,7 @@ struct PlanLayout {
         off_qhi = o;  o += pad128(bh * nK);
         off_qmono = o; o += pad128(bh * nQ);
         off_kmono = o; o += pad128(bh * nK);
+        off_ctr = o;   o += 128;
         total = o;
     }
 };
@@ -63,6 +67,8 @@ struct MaskArgs {
     int M, N, gap, causal, mode;
     int He;               // 1 or H
 };
+
+enum { CTR_FWD = 0, CTR_DKDV = 2, CTR_DQ = 4 };  // pairs {next item, CTAs finished} inside the plan's ctr section
 
 enum : uint32_t {
     TILE_VISIT = 1u,   // at least one entry may be unmasked

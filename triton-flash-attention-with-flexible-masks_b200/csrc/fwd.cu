@@ -44,11 +44,11 @@ struct FwdSmem {
     static constexpr int off_qc = off_list + 2 * kListCap * 2;  // int32  [2][128] query codes
     static constexpr int off_kc = off_qc + 2 * kBlk * 4;        // int32  [NKC][128] key codes, loaded with K
     static constexpr int off_ml = off_kc + NKC * kBlk * 4;      // float  [2][2 groups][m, l][128]
-    static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][4]: T, lo
+    static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][4]: T, lo, item (-1: no more items)
     static constexpr int off_bar = off_info + 32;
     // item_full[2] item_empty[2] q_full[2] o_staged[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
-    // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] kc_full[NKC]
-    static constexpr int n_bar = 8 + 4 * NS + 12 + 8;
+    // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] kc_full[NKC] ml_full
+    static constexpr int n_bar = 8 + 4 * NS + 12 + 8 + 1;
     static constexpr int off_misc = off_bar + n_bar * 8;  // tmem slot, abort flag
     static constexpr int total = off_misc + 16;
 };
@@ -68,6 +68,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int nQ = mk.L.nQ;
     const int HB = p.H * p.B;
     const int n_items = nQ * HB;
+    unsigned int* ctr = (mk.mode == 1) ? reinterpret_cast<unsigned int*>(const_cast<int32_t*>(mk.plan) + mk.L.off_ctr) + CTR_FWD : nullptr;
 
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);  // [0] tmem, [1] abort
     volatile int* info = reinterpret_cast<volatile int*>(smem + S::off_info);
@@ -75,7 +76,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
     constexpr int B_ITEMFULL = 0, B_ITEMEMPTY = 2, B_QFULL = 4, B_OSTAGED = 6, B_KFULL = 8, B_KEMPTY = 8 + NS,
                   B_VFULL = 8 + 2 * NS, B_VEMPTY = 8 + 3 * NS, B_SFULL = 8 + 4 * NS, B_PHALF0 = B_SFULL + 2,
-                  B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_KCFULL = B_SFULL + 12;
+                  B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_KCFULL = B_SFULL + 12,
+                  B_MLFULL = B_KCFULL + S::NKC;
     Abort ab{misc + 1, p.status};
 
     if (tid == 0) {
@@ -92,6 +94,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             mbar_init(BAR(B_OFREE + s), 256);
         }
         for (int s = 0; s < S::NKC; ++s) mbar_init(BAR(B_KCFULL + s), 1);
+        mbar_init(BAR(B_MLFULL), 256);
         for (int s = 0; s < NS; ++s) {
             mbar_init(BAR(B_KFULL + s), 1);
             mbar_init(BAR(B_KEMPTY + s), 1);
@@ -129,13 +132,28 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             // a previous kernel reported an error: do nothing
         } else if (warp == 11) {
             // ------------------------------ item scheduler ------------------------------
+            // Items are handed out in order from a counter in the plan (any CTA takes the next one: the
+            // work per item varies with the document layout); without a plan (no id mask) the items
+            // are sorted by length and dealt out in alternating direction, which balances as well.
             bool ok = true;
-            int k = 0;
-            for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+            for (int k = 0;; ++k) {
                 const int s = k & 1, use = k >> 1;
                 if (use > 0) ok = mbar_wait(BAR(B_ITEMEMPTY + s), (use - 1) & 1, ab, ST_WAIT_TIMEOUT + 11);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                int j = 0;
+                if (lane == 0) {
+                    if (ctr) j = int(atomicAdd(ctr, 1u));
+                    else j = k * int(gridDim.x) + ((k & 1) ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x));
+                }
+                j = __shfl_sync(0xffffffffu, j, 0);
+                if (j >= n_items) {  // end marker
+                    if (lane == 0) {
+                        info[s * 4 + 2] = -1;
+                        mbar_arrive(BAR(B_ITEMFULL + s));
+                    }
+                    break;
+                }
                 int qb, h, b;
                 decode(j, qb, h, b);
                 const int he = (mk.He == 1) ? 0 : h;
@@ -160,6 +178,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 if (lane == 0) {
                     info[s * 4 + 0] = T;
                     info[s * 4 + 1] = lo;
+                    info[s * 4 + 2] = j;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(B_ITEMFULL + s));
@@ -173,21 +192,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 bool ok = true;
                 int k = 0, G = 0;  // G: tiles of all earlier items (the K / V rings run across items)
                 // TMA store of the O tile the softmax groups staged in slot (kk & 1) for item kk
+                int item_of[2] = {0, 0};  // the items in the two slots
                 auto store_o = [&](int kk) {
                     const int s = kk & 1;
                     if (!mbar_wait(BAR(B_OSTAGED + s), (kk >> 1) & 1, ab, ST_WAIT_TIMEOUT + 13)) return false;
                     int qb, h, b;
-                    decode(int(blockIdx.x) + kk * int(gridDim.x), qb, h, b);
+                    decode(item_of[s], qb, h, b);
                     for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmO, sQ(s) + x * S::BOX, x * 64, qb * kBlk, h, b);
                     tma_store_commit();
                     tma_store_wait_read();
                     return true;
                 };
-                for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+                for (;; ++k) {
                     const int s = k & 1, use = k >> 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
                     if (!ok) break;
-                    const int T = info[s * 4 + 0], lo = info[s * 4 + 1];
+                    const int T = info[s * 4 + 0], lo = info[s * 4 + 1], j = info[s * 4 + 2];
+                    if (j < 0) break;
                     const uint16_t* list = list_of(s);
                     int qb, h, b;
                     decode(j, qb, h, b);
@@ -196,6 +217,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     // the slot still holds the staged O tile of item k-2: send it off first
                     if (use > 0) ok = store_o(k - 2);
                     if (!ok) break;
+                    item_of[s] = j;
                     mbar_expect_tx(BAR(B_QFULL + s), S::TILE);
                     for (int x = 0; x < S::NBOX; ++x)
                         tma_load_4d(sQ(s) + x * S::BOX, &tmQ, BAR(B_QFULL + s), x * 64, qb * kBlk, h, b);
@@ -255,11 +277,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 const uint32_t tO = tmem + 256u + uint32_t(w) * uint32_t(D);
                 bool ok = true;
                 int k = 0, G = 0, cw = 0;  // cw: tiles this chain has finished (phases of its barriers)
-                for (int j = blockIdx.x; j < n_items && ok; j += gridDim.x, ++k) {
+                for (;; ++k) {
                     const int s = k & 1, use = k >> 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
                     if (!ok) break;
                     const int T = info[s * 4 + 0];
+                    if (info[s * 4 + 2] < 0) break;
                     ok = mbar_wait(BAR(B_QFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 3);
                     if (!ok) break;
                     const uint32_t q_tile = sQ(s);
@@ -323,8 +346,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     } else {
         setmaxnreg_inc<216>();
         // ------------------------------ softmax groups ------------------------------
-        // Every thread walks all items and takes part in both named barriers of every item, even
-        // after a wait has been given up (alive == false), so that no thread is ever left waiting.
+        // Every wait is a bounded mbarrier wait: a thread whose wait was given up (alive == false)
+        // leaves the item loop at once, and nobody is left waiting for it for longer than the limit.
         const int w = warp >> 2;  // group
         const int r = tid & 127;  // row inside the block
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
@@ -335,14 +358,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         int k = 0, cw = 0;  // cw: tiles this group has finished (phases of its barriers)
         int nturn = 0;      // turns this group has taken (phase of its turn barrier)
         int G = 0;          // tiles of all earlier items (stage / phase of the K and V rings)
-        for (int j = blockIdx.x; j < n_items; j += gridDim.x, ++k) {
+        for (; alive; ++k) {
             const int s = k & 1, use = k >> 1;
-            if (alive) {
-                alive = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
-                alive = __all_sync(0xffffffffu, alive);
-            }
-            const int T = alive ? info[s * 4 + 0] : 0;
-            const int lo = alive ? info[s * 4 + 1] : 0;
+            alive = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            const int T = info[s * 4 + 0];
+            const int lo = info[s * 4 + 1];
+            const int j = info[s * 4 + 2];
+            if (j < 0) break;
             if (r == 0) FA_TRACE_EV(w, 32 + (T > 63 ? 63 : T));
             const uint16_t* list = list_of(s);
             int qb, h, b;
@@ -516,16 +540,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             // ------------------------------ item epilogue ------------------------------
             // wait for this group's last P*V, then merge the two partial softmaxes
             if (r == 0) FA_TRACE_EV(w, 1);
-            if (alive && n_my > 0) {
+            if (!alive) break;
+            if (n_my > 0) {
                 alive = mbar_wait(BAR(B_PVDONE + w), (cw - 1) & 1, ab, ST_WAIT_TIMEOUT + 9);
                 alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
             }
             float* ml = reinterpret_cast<float*>(smem + S::off_ml) + s * (4 * kBlk);  // [2 groups][m, l][128]
             ml[(w * 2 + 0) * kBlk + r] = m_run;
             ml[(w * 2 + 1) * kBlk + r] = l_run;
             if (r == 0) FA_TRACE_EV(w, 2);
             tc_fence_before();
-            named_bar_sync(1, 256);  // both groups are past all MMAs of this item
+            mbar_arrive(BAR(B_MLFULL));  // both groups are past all MMAs of this item
+            alive = mbar_wait(BAR(B_MLFULL), k & 1, ab, ST_WAIT_TIMEOUT + 16);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
             tc_fence_after();
             if (r == 0) FA_TRACE_EV(w, 3);
             const float m0 = ml[0 * kBlk + r], l0 = ml[1 * kBlk + r];
@@ -600,6 +629,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
+    }
+    // the last CTA to leave clears the work counters for the next launch that uses this plan
+    if (tid == 0 && ctr) {
+        __threadfence();
+        if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) {
+            ctr[0] = 0;
+            ctr[1] = 0;
+        }
     }
 }
 

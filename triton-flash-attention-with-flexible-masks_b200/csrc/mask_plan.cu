@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(128) plan_codes_kernel(IdsView eq, IdsView ek,
         }
         plan[L.off_kc + bh * L.Npad + l] = code;
     }
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) plan[L.off_ctr + threadIdx.x] = 0;
     const int mn = block_reduce_min(valid ? code : 0x7fffffff, scratch);
     const int mx = block_reduce_max(valid ? code : int(-2147483647 - 1), scratch);
     // monotone within the block (valid entries): no rise or no fall between neighbours

@@ -28,7 +28,7 @@ struct DkdvParams {
     const float* lse;    // [B, H, Mpad]
     const float* delta;  // [B, H, Mpad]
     MaskArgs mask;
-    int H, Hk, G;
+    int B, H, Hk, G;
     float scale_log2, sm_scale;
     int* status;
 };
