@@ -107,15 +107,20 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int G = p.G;
     const int nK = mk.L.nK;
     const int n_items = nK * p.Hk * p.B;
-    // item -> (key block, kv head, batch), key block slowest: with a causal mask the first key blocks
-    // are the long ones, and round robin over items sorted by length balances the CTAs
-    const int HB = p.Hk * p.B;
     unsigned int* ctr = (mk.mode == 1) ? reinterpret_cast<unsigned int*>(const_cast<int32_t*>(mk.plan) + mk.L.off_ctr) + CTR_DKDV : nullptr;
+    // item -> (key block, kv head, batch). Heads are taken in groups of p.gh; inside a group the key
+    // blocks go in order (with a causal mask: long ones first) and the heads of the group vary
+    // fastest. The CTAs thus work on neighbouring key blocks of a few heads at a time: few enough
+    // that their Q / dO streams stay in L2, enough that not all CTAs pull the same lines.
+    const int HB = p.Hk * p.B;
     auto decode = [&](int j, int& kb, int& hk, int& b) {
-        kb = j / HB;
-        const int t = j - kb * HB;
-        hk = t % p.Hk;
-        b = t / p.Hk;
+        const int per = p.gh * nK;
+        const int grp = j / per, rem = j - grp * per;
+        const int gsz = min(p.gh, HB - grp * p.gh);
+        const int pos = rem / gsz, bh = grp * p.gh + (rem - pos * gsz);
+        kb = pos;
+        hk = bh % p.Hk;
+        b = bh / p.Hk;
     };
 
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);
@@ -177,8 +182,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             // Item k goes to slot k & 1: range [lo, lo + n) of candidate query blocks (union over the
             // group's heads), a 2-bit code per candidate, and the number of tiles.
             // Items are handed out in order from a counter in the plan (any CTA takes the next one: the
-            // work per item varies with the document layout); without a plan (no id mask) the items
-            // are sorted by length and dealt out in alternating direction, which balances as well.
+            // work per item varies with the document layout); without a plan (no id mask) they are
+            // dealt out round robin in alternating direction, which evens out their sorted lengths.
             bool ok = true;
             for (int k = 0;; ++k) {
                 const int s = k & 1, use = k >> 1;

@@ -118,10 +118,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };
     auto sV = [&](int s) { return sbase + S::off_v + uint32_t(s) * S::TILE; };
     auto list_of = [&](int s) { return reinterpret_cast<const uint16_t*>(smem + S::off_list) + s * kListCap; };
-    // item index -> (query block, head, batch): heads and batches vary fastest, long causal rows first
+    // item -> (query block, head, batch). Heads are taken in groups of p.gh; inside a group the query
+    // blocks go from the last one down (with a causal mask: long ones first) and the heads of the
+    // group vary fastest. The CTAs thus work on neighbouring query blocks of a few heads at a time:
+    // few enough that their K / V streams stay in L2, enough that not all CTAs pull the same lines.
     auto decode = [&](int j, int& qb, int& h, int& b) {
-        const int rank = j / HB, bh = j - rank * HB;
-        qb = nQ - 1 - rank;
+        const int per = p.gh * nQ;                 // items of a full group of heads
+        const int grp = j / per, rem = j - grp * per;
+        const int gsz = min(p.gh, HB - grp * p.gh);  // heads in this group (the last one may be smaller)
+        const int pos = rem / gsz, bh = grp * p.gh + (rem - pos * gsz);
+        qb = nQ - 1 - pos;
         b = bh / p.H;
         h = bh - b * p.H;
     };
@@ -133,8 +139,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         } else if (warp == 11) {
             // ------------------------------ item scheduler ------------------------------
             // Items are handed out in order from a counter in the plan (any CTA takes the next one: the
-            // work per item varies with the document layout); without a plan (no id mask) the items
-            // are sorted by length and dealt out in alternating direction, which balances as well.
+            // work per item varies with the document layout); without a plan (no id mask) they are
+            // dealt out round robin in alternating direction, which evens out their sorted lengths.
             bool ok = true;
             for (int k = 0;; ++k) {
                 const int s = k & 1, use = k >> 1;

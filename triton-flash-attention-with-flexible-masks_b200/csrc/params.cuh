@@ -12,6 +12,7 @@ struct FwdParams {
     float* lse;  // [B, H, Mpad], log2 domain
     MaskArgs mask;
     int H, B, G;
+    int gh;            // heads per scheduling group
     float scale_log2;  // sm_scale * log2(e)
     int* status;
 };
@@ -29,6 +30,7 @@ struct DkdvParams {
     const float* delta;  // [B, H, Mpad]
     MaskArgs mask;
     int B, H, Hk, G;
+    int gh;  // kv heads per scheduling group
     float scale_log2, sm_scale;
     int* status;
 };
@@ -37,7 +39,8 @@ struct DqParams {
     const float* lse;
     const float* delta;
     MaskArgs mask;
-    int H, G;
+    int B, H, G;
+    int gh;  // heads per scheduling group
     float scale_log2, sm_scale;
     int* status;
 };
