@@ -72,18 +72,25 @@ const char* fa_error_string(int code);
 /* Rows of the internal per-row fp32 buffers (log-sum-exp, delta): M rounded up to 128. */
 int64_t fa_padded_rows(int32_t M);
 
-/* Size in bytes of the mask plan for this problem (0 when mode == FA_MODE0_NOPE). */
+/* Size in bytes of the mask plan for this problem (when mode == FA_MODE0_NOPE: 512 bytes, the work
+ * counters of the attention kernels only; such a plan is optional). */
 int fa_plan_bytes(const fa_problem* p, size_t* bytes);
 
 /* Builds the mask plan from eq [B,H,M] / ek [B,H,N]: 32-bit id codes, per-128-block id
- * min/max, and per-block ranges of blocks that hold at least one unmasked entry.
+ * min/max, per-block ranges of blocks that hold at least one unmasked entry, and a few work
+ * counters through which the CTAs of fa_fwd / fa_bwd_dkdv / fa_bwd_dq share out their work.
+ * The attention kernels update those counters (although they take the plan as `const void*`) and
+ * leave them zero, so a plan can be used any number of times, but only by one launch of each of
+ * the three at a time.
  * Mask rule (flash_triton.py:114, README.md:16): keep = (eq >= 0) | (eq == ek). */
 int fa_plan_build(const fa_problem* p, const fa_ids* eq, const fa_ids* ek, void* plan, size_t plan_bytes,
                   int32_t* status, void* stream);
 
 /* Forward (replaces flash_triton.py:541). o has q's shape; lse is [B, H, fa_padded_rows(M)] fp32,
  * log2-domain log-sum-exp of the scaled scores (flash_triton.py:133), -inf for a row with no
- * unmasked key (whose output row is 0). plan may be NULL when mode == FA_MODE0_NOPE. */
+ * unmasked key (whose output row is 0). plan may be NULL when mode == FA_MODE0_NOPE (here and in
+ * the backward entry points): the CTAs then share out their work in a fixed order instead of through
+ * the plan's counters, which costs a few percent when the work per block is uneven. */
 int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
            const fa_tensor* o, float* lse, const void* plan, int32_t* status, void* stream);
 

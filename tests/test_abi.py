@@ -53,7 +53,7 @@ def test_plan_bytes():
     assert lib.fa_plan_bytes(ctypes.byref(_prob()), ctypes.byref(n)) == 0
     # codes for 256 queries + 256 keys, plus ten per-block arrays padded to 128 entries
     assert n.value == 4 * (256 + 256 + 10 * 128 + 128)  # codes, block statistics and ranges, work counters
-    assert lib.fa_plan_bytes(ctypes.byref(_prob(mode=0)), ctypes.byref(n)) == 0 and n.value == 0
+    assert lib.fa_plan_bytes(ctypes.byref(_prob(mode=0)), ctypes.byref(n)) == 0 and n.value == 4 * 128  # counters only
 
 
 @pytest.mark.parametrize("kw,code", [

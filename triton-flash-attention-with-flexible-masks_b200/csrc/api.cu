@@ -87,11 +87,16 @@ int make_map(CUtensorMap* out, const fa_tensor* t, int dtype, int B, int H, int 
     return r == CUDA_SUCCESS ? FA_OK : FA_ERR_TENSORMAP;
 }
 
+constexpr size_t kCtrWords = 128;  // size of the plan's counter section (PlanLayout::off_ctr)
+
 int make_mask(fa::MaskArgs* m, const fa_problem* p, const void* plan) {
     if (p->mode == FA_MODE1_DOC && !plan) return FA_ERR_PLAN_SIZE;
     m->plan = (p->mode == FA_MODE1_DOC) ? static_cast<const int32_t*>(plan) : nullptr;
     m->He = (p->mode == FA_MODE1_DOC) ? p->id_heads : 1;
     m->L = fa::PlanLayout(p->B, m->He, p->M, p->N);
+    // the kernels count in the plan although the entry points take it as const: see fa_plan_build in the header
+    unsigned int* words = static_cast<unsigned int*>(const_cast<void*>(plan));
+    m->ctr = !plan ? nullptr : (p->mode == FA_MODE1_DOC) ? words + m->L.off_ctr : words;
     m->M = p->M;
     m->N = p->N;
     m->gap = p->N > p->M ? p->N - p->M : 0;  // flash_triton.py:521
@@ -105,12 +110,20 @@ fa::OutTensor out_view(const fa_tensor* t) { return fa::OutTensor{t->ptr, t->str
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Number of SMs of the current device (persistent kernels launch one CTA per SM); cached per device.
-// Heads per scheduling group of the persistent kernels (see their `decode`). Measured on B200: with
-// 32 heads of 32768 tokens (packed documents) and with 16 heads of 8192 tokens, interleaving all heads
-// is fastest; with hundreds of short heads groups of 8 to 64 are within a few percent of each other
-// and one group of all heads is 30 % slower (their streams no longer fit in L2).
-int head_group(int heads_total) {
-    const int gh = 32;
+// Heads per scheduling group of the persistent kernels (see their `decode`): as many heads as
+// stream through L2 side by side without evicting each other. Measured on B200 (126 MB L2):
+//  - document masks (32 heads x 32768 tokens, 64 documents): a CTA only streams the blocks of its own
+//    document, and interleaving all 32 heads is fastest (groups of 1 head: 8 % slower, all CTAs pull
+//    the same lines at once);
+//  - no id mask, 512 heads x 8192 tokens, D = 128: groups of 8 heads (32 MB of K + V) are 14 % faster
+//    than groups of 32 and draw less power; hundreds of 2048-token heads in one group: 30 % slower.
+int head_group(const fa_problem* p, int heads_total) {
+    int gh = 32;
+    if (p->mode == FA_MODE0_NOPE) {
+        const int64_t per_head = int64_t(p->M > p->N ? p->M : p->N) * p->D * 2 * 2;  // two streamed tensors
+        const int64_t fit = (int64_t(32) << 20) / (per_head > 0 ? per_head : 1);
+        gh = fit < 1 ? 1 : fit > 32 ? 32 : int(fit);
+    }
     return gh < heads_total ? gh : heads_total;
 }
 
@@ -159,7 +172,7 @@ int fa_plan_bytes(const fa_problem* p, size_t* bytes) {
     const int rc = check_problem(p);
     if (rc) return rc;
     if (p->mode == FA_MODE0_NOPE) {
-        *bytes = 0;
+        *bytes = kCtrWords * sizeof(int32_t);  // the work counters only
         return FA_OK;
     }
     fa::PlanLayout L(p->B, p->id_heads, p->M, p->N);
@@ -171,7 +184,13 @@ int fa_plan_build(const fa_problem* p, const fa_ids* eq, const fa_ids* ek, void*
                   int32_t* status, void* stream) {
     const int rc = check_problem(p);
     if (rc) return rc;
-    if (p->mode != FA_MODE1_DOC) return FA_OK;
+    if (p->mode != FA_MODE1_DOC) {  // no mask data: the plan is the work counters, cleared here
+        if (!plan) return FA_OK;
+        if (reinterpret_cast<uintptr_t>(plan) % 16 != 0) return FA_ERR_ALIGNMENT;
+        if (plan_bytes < kCtrWords * sizeof(int32_t)) return FA_ERR_PLAN_SIZE;
+        return cudaMemsetAsync(plan, 0, kCtrWords * sizeof(int32_t), static_cast<cudaStream_t>(stream)) == cudaSuccess
+                   ? FA_OK : FA_ERR_LAUNCH;
+    }
     if (!eq || !ek || !eq->ptr || !ek->ptr || !plan || !status) return FA_ERR_BAD_ARG;
     if ((eq->dtype != FA_ID_INT32 && eq->dtype != FA_ID_INT64) || (ek->dtype != FA_ID_INT32 && ek->dtype != FA_ID_INT64))
         return FA_ERR_BAD_ARG;
@@ -207,7 +226,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     fp.H = p->H;
     fp.B = p->B;
     fp.G = p->H / p->Hk;
-    fp.gh = head_group(p->H * p->B);
+    fp.gh = head_group(p, p->H * p->B);
     fp.scale_log2 = p->sm_scale * kLog2e;
     fp.status = status;
     const cudaError_t e =
@@ -260,7 +279,7 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     kp.H = p->H;
     kp.Hk = p->Hk;
     kp.G = p->H / p->Hk;
-    kp.gh = head_group(p->Hk * p->B);
+    kp.gh = head_group(p, p->Hk * p->B);
     kp.scale_log2 = p->sm_scale * kLog2e;
     kp.sm_scale = p->sm_scale;
     kp.status = status;
@@ -297,7 +316,7 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     qp.B = p->B;
     qp.H = p->H;
     qp.G = p->H / p->Hk;
-    qp.gh = head_group(p->H * p->B);
+    qp.gh = head_group(p, p->H * p->B);
     qp.scale_log2 = p->sm_scale * kLog2e;
     qp.sm_scale = p->sm_scale;
     qp.status = status;

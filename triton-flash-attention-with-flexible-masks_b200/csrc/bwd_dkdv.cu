@@ -107,7 +107,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int G = p.G;
     const int nK = mk.L.nK;
     const int n_items = nK * p.Hk * p.B;
-    unsigned int* ctr = (mk.mode == 1) ? reinterpret_cast<unsigned int*>(const_cast<int32_t*>(mk.plan) + mk.L.off_ctr) + CTR_DKDV : nullptr;
+    unsigned int* ctr = mk.ctr ? mk.ctr + CTR_DKDV : nullptr;
     // item -> (key block, kv head, batch). Heads are taken in groups of p.gh; inside a group the key
     // blocks go in order (with a causal mask: long ones first) and the heads of the group vary
     // fastest. The CTAs thus work on neighbouring key blocks of a few heads at a time: few enough
@@ -182,7 +182,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             // Item k goes to slot k & 1: range [lo, lo + n) of candidate query blocks (union over the
             // group's heads), a 2-bit code per candidate, and the number of tiles.
             // Items are handed out in order from a counter in the plan (any CTA takes the next one: the
-            // work per item varies with the document layout); without a plan (no id mask) they are
+            // work per item varies with the mask); without counters (no plan given) they are
             // dealt out round robin in alternating direction, which evens out their sorted lengths.
             bool ok = true;
             for (int k = 0;; ++k) {

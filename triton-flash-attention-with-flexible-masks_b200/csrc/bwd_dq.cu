@@ -76,7 +76,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int nQ = mk.L.nQ;
     const int HB = p.H * p.B;
     const int n_items = nQ * HB;
-    unsigned int* ctr = (mk.mode == 1) ? reinterpret_cast<unsigned int*>(const_cast<int32_t*>(mk.plan) + mk.L.off_ctr) + CTR_DQ : nullptr;
+    unsigned int* ctr = mk.ctr ? mk.ctr + CTR_DQ : nullptr;
     // item -> (query block, head, batch). Heads are taken in groups of p.gh; inside a group the query
     // blocks go from the last one down (with a causal mask: long ones first) and the heads of the
     // group vary fastest. The CTAs thus work on neighbouring query blocks of a few heads at a time:
@@ -142,7 +142,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             // Item k goes to slot k & 1: range [lo, lo + n) of candidate key blocks, a 2-bit code per
             // candidate, the number of visited tiles, the item index (-1: no more items). Items are
             // handed out in order from a counter in the plan (any CTA takes the next one: the work
-            // per item varies with the document layout); without a plan (no id mask) they are dealt out
+            // per item varies with the mask); without counters (no plan given) they are dealt out
             // round robin in alternating direction, which evens out their sorted lengths.
             bool ok = true;
             for (int k = 0;; ++k) {

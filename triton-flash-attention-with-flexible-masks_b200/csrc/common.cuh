@@ -63,6 +63,7 @@ struct PlanLayout {
 // What every attention kernel needs to evaluate the mask.
 struct MaskArgs {
     const int32_t* plan;  // null when mode == 0
+    unsigned int* ctr;    // work counters (CTR_* pairs), or null: the persistent kernels then share out items statically
     PlanLayout L;
     int M, N, gap, causal, mode;
     int He;               // 1 or H

@@ -68,7 +68,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int nQ = mk.L.nQ;
     const int HB = p.H * p.B;
     const int n_items = nQ * HB;
-    unsigned int* ctr = (mk.mode == 1) ? reinterpret_cast<unsigned int*>(const_cast<int32_t*>(mk.plan) + mk.L.off_ctr) + CTR_FWD : nullptr;
+    unsigned int* ctr = mk.ctr ? mk.ctr + CTR_FWD : nullptr;
 
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);  // [0] tmem, [1] abort
     volatile int* info = reinterpret_cast<volatile int*>(smem + S::off_info);
@@ -139,7 +139,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         } else if (warp == 11) {
             // ------------------------------ item scheduler ------------------------------
             // Items are handed out in order from a counter in the plan (any CTA takes the next one: the
-            // work per item varies with the document layout); without a plan (no id mask) they are
+            // work per item varies with the mask); without counters (no plan given) they are
             // dealt out round robin in alternating direction, which evens out their sorted lengths.
             bool ok = true;
             for (int k = 0;; ++k) {

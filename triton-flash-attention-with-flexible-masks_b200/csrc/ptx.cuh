@@ -320,28 +320,3 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 }  // namespace fa
-
-namespace fa {
-// exp2 of two values on the FMA pipe (no MUFU): round-to-nearest split x = n + f, f in [-0.5, 0.5],
-// cubic for 2^f (max relative error 7.5e-5, below the bf16 / fp16 rounding of P), exponent
-// added as an integer. x is clamped at -126, so the result is never exactly 0: only for tiles
-// without masked entries.
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
-    float x0, x1;
-    unpack_f2(x2, x0, x1);
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    const uint64_t xc = pack_f2(x0, x1);
-    const uint64_t t = add_f2(xc, pack_f2(12582912.0f, 12582912.0f));  // 1.5 * 2^23: n lands in the low mantissa bits
-    const uint64_t xr = add_f2(t, pack_f2(-12582912.0f, -12582912.0f));
-    const uint64_t f = fma_f2(xr, pack_f2(-1.0f, -1.0f), xc);
-    uint64_t y = fma_f2(pack_f2(0.05517165f, 0.05517165f), f, pack_f2(0.24261113f, 0.24261113f));
-    y = fma_f2(y, f, pack_f2(0.69326097f, 0.69326097f));
-    y = fma_f2(y, f, pack_f2(0.99992806f, 0.99992806f));
-    float y0, y1, t0, t1;
-    unpack_f2(y, y0, y1);
-    unpack_f2(t, t0, t1);
-    p0 = __int_as_float(__float_as_int(y0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(y1) + (__float_as_int(t1) << 23));
-}
-}  // namespace fa

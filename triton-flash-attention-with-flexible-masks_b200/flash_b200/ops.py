@@ -130,11 +130,16 @@ def _stream():
 
 
 def build_plan(prob, eq, ek, status):
-    """Mask plan for (eq, ek): int32 device buffer consumed by the forward and backward kernels."""
+    """Mask plan: int32 device buffer consumed by the forward and backward kernels. With ids it
+    holds their codes and block statistics; without (eq is None) only the kernels' work counters."""
     lib = _lib.load()
     nbytes = ctypes.c_size_t(0)
     _lib.check(lib.fa_plan_bytes(ctypes.byref(prob), ctypes.byref(nbytes)), "fa_plan_bytes")
-    plan = torch.empty(max(nbytes.value // 4, 1), dtype=torch.int32, device=eq.device)
+    plan = torch.empty(max(nbytes.value // 4, 1), dtype=torch.int32, device=status.device)
+    if eq is None:
+        _lib.check(lib.fa_plan_build(ctypes.byref(prob), None, None, plan.data_ptr(), nbytes.value,
+                                     status.data_ptr(), _stream()), "fa_plan_build")
+        return plan
     ieq, iek = _ids(eq), _ids(ek)
     with _Timed("plan", 2):
         _lib.check(lib.fa_plan_build(ctypes.byref(prob), ctypes.byref(ieq), ctypes.byref(iek), plan.data_ptr(),
@@ -181,9 +186,10 @@ class FlashAttention(torch.autograd.Function):
         with torch.cuda.device(q.device):
             prob = _problem(B, H, Hk, M, N, D, q.dtype, causal, score_func_mode, id_heads, sm_scale)
             status = _status_word(q.device)
-            plan = None
             if score_func_mode == SCORE_FUNC_MODE1_DOC:
                 plan = build_plan(prob, eq, ek, status)
+            else:
+                plan = build_plan(prob, None, None, status)
             Out = torch.empty_like(q)
             if maybe_contiguous(Out) is not Out:
                 Out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
