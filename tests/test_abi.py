@@ -51,8 +51,8 @@ def test_plan_bytes():
     lib = _lib.load()
     n = ctypes.c_size_t(0)
     assert lib.fa_plan_bytes(ctypes.byref(_prob()), ctypes.byref(n)) == 0
-    # codes for 256 queries + 256 keys, plus ten per-block arrays padded to 128 entries
-    assert n.value == 4 * (256 + 256 + 10 * 128 + 128)  # codes, block statistics and ranges, work counters
+    # codes for 256 queries + 256 keys, plus twelve per-block arrays padded to 128 entries and the counters
+    assert n.value == 4 * (256 + 256 + 12 * 128 + 128)  # codes; block statistics, ranges, sorted orders; work counters
     assert lib.fa_plan_bytes(ctypes.byref(_prob(mode=0)), ctypes.byref(n)) == 0 and n.value == 4 * 128  # counters only
 
 

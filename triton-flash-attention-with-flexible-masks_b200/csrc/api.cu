@@ -227,6 +227,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     fp.B = p->B;
     fp.G = p->H / p->Hk;
     fp.gh = head_group(p, p->H * p->B);
+    fp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 64 * int64_t(sms)) ? 1 : 0;
     fp.scale_log2 = p->sm_scale * kLog2e;
     fp.status = status;
     const cudaError_t e =
@@ -273,6 +274,8 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     CUtensorMap tdk, tdv;
     if ((rc = make_map(&tdk, dk, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     if ((rc = make_map(&tdv, dv, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
+    const int sms = sm_count();
+    if (sms <= 0) return FA_ERR_LAUNCH;
     kp.lse = lse;
     kp.delta = delta;
     kp.B = p->B;
@@ -280,11 +283,10 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     kp.Hk = p->Hk;
     kp.G = p->H / p->Hk;
     kp.gh = head_group(p, p->Hk * p->B);
+    kp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->N, fa::kBlk) * p->Hk * p->B) < 64 * int64_t(sms)) ? 1 : 0;
     kp.scale_log2 = p->sm_scale * kLog2e;
     kp.sm_scale = p->sm_scale;
     kp.status = status;
-    const int sms = sm_count();
-    if (sms <= 0) return FA_ERR_LAUNCH;
     const cudaError_t e =
         fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdk, tdv, kp, sms,
                             static_cast<cudaStream_t>(stream));
@@ -311,17 +313,18 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     if ((rc = make_map(&tv, v, p->dtype, p->B, p->Hk, p->N, p->D))) return rc;
     CUtensorMap tdq;
     if ((rc = make_map(&tdq, dq, p->dtype, p->B, p->H, p->M, p->D))) return rc;
+    const int sms = sm_count();
+    if (sms <= 0) return FA_ERR_LAUNCH;
     qp.lse = lse;
     qp.delta = delta;
     qp.B = p->B;
     qp.H = p->H;
     qp.G = p->H / p->Hk;
     qp.gh = head_group(p, p->H * p->B);
+    qp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 64 * int64_t(sms)) ? 1 : 0;
     qp.scale_log2 = p->sm_scale * kLog2e;
     qp.sm_scale = p->sm_scale;
     qp.status = status;
-    const int sms = sm_count();
-    if (sms <= 0) return FA_ERR_LAUNCH;
     const cudaError_t e =
         fa::launch_bwd_dq(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdq, qp, sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;

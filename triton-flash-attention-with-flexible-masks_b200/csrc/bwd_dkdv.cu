@@ -118,9 +118,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int grp = j / per, rem = j - grp * per;
         const int gsz = min(p.gh, HB - grp * p.gh);
         const int pos = rem / gsz, bh = grp * p.gh + (rem - pos * gsz);
-        kb = pos;
         hk = bh % p.Hk;
         b = bh / p.Hk;
+        // few items per CTA: longest first (sorted in the plan), so that no long item is left for the end
+        kb = p.by_length ? mk.plan[mk.L.off_ordk + (int64_t(b) * mk.He + (mk.He == 1 ? 0 : hk * G)) * nK + pos] : pos;
     };
 
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);

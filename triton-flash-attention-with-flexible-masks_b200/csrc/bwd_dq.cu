@@ -86,9 +86,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const int grp = j / per, rem = j - grp * per;
         const int gsz = min(p.gh, HB - grp * p.gh);  // heads in this group (the last one may be smaller)
         const int pos = rem / gsz, bh = grp * p.gh + (rem - pos * gsz);
-        qb = nQ - 1 - pos;
         b = bh / p.H;
         h = bh - b * p.H;
+        // few items per CTA: longest first (sorted in the plan), so that no long item is left for the end
+        qb = p.by_length ? mk.plan[mk.L.off_ordq + (int64_t(b) * mk.He + (mk.He == 1 ? 0 : h)) * nQ + pos] : nQ - 1 - pos;
     };
 
     volatile int* misc = reinterpret_cast<volatile int*>(smem + S::off_misc);

@@ -11,6 +11,7 @@
 namespace fa {
 
 constexpr int kBlk = 128;  // rows of a query block = keys of a key block, for every kernel
+constexpr int kListCap = 1024;  // blocks per sequence (per-item tile lists live in shared memory)
 
 // Query code of an id >= 0 ("attends to everything"). Key codes are never positive.
 constexpr int32_t kCodeAny = 0x7fffffff;
@@ -27,13 +28,15 @@ __host__ __device__ inline int64_t pad128(int64_t x) { return (x + 127) / 128 * 
 //   q_lo, q_hi   [B, He, nK] range of query blocks with an unmasked entry, per key block
 //   qmono [B, He, nQ], kmono [B, He, nK]  1 if the codes of the block are monotone (non-decreasing or
 //                non-increasing), i.e. equal codes are adjacent: the usual packed-documents layout
+//   ord_q [B, He, nQ], ord_k [B, He, nK]  the blocks of a head sorted by the length of their visit range,
+//                longest first (ties: from the long end of a causal head)
 //   ctr [128]    work counters of the persistent kernels (item counter, finished-CTA counter per kernel);
 //                zero between launches: the plan build clears them and every kernel clears its pair
 //                when its last CTA leaves, so a plan serves one launch of each kernel at a time
 struct PlanLayout {
     int B, He, M, N, nQ, nK;
     int64_t Mpad, Npad;
-    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi, off_qmono, off_kmono, off_ctr;
+    int64_t off_qc, off_kc, off_qmin, off_qmax, off_kmin, off_kmax, off_kvlo, off_kvhi, off_qlo, off_qhi, off_qmono, off_kmono, off_ordq, off_ordk, off_ctr;
     int64_t total;  // int32 elements
 
     __host__ __device__ PlanLayout() {}
@@ -55,6 +58,8 @@ struct PlanLayout {
         off_qhi = o;  o += pad128(bh * nK);
         off_qmono = o; o += pad128(bh * nQ);
         off_kmono = o; o += pad128(bh * nK);
+        off_ordq = o;  o += pad128(bh * nQ);
+        off_ordk = o;  o += pad128(bh * nK);
         off_ctr = o;   o += 128;
         total = o;
     }

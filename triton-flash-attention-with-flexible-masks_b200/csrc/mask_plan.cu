@@ -134,6 +134,33 @@ __global__ void __launch_bounds__(128) plan_ranges_kernel(int32_t* plan, PlanLay
     }
 }
 
+// grid (2, He, B), 1024 threads: the blocks of one head sorted by the length of their visit range,
+// longest first; equal lengths keep the order "from the long end" (last query block first, first key
+// block first). Rank by counting: block i goes to the position given by the number of blocks that
+// come before it.
+__global__ void __launch_bounds__(1024) plan_order_kernel(int32_t* plan, PlanLayout L) {
+    __shared__ int len[kListCap];
+    const bool is_q = blockIdx.x == 0;
+    const int he = blockIdx.y, b = blockIdx.z;
+    const int64_t bh = int64_t(b) * L.He + he;
+    const int n = is_q ? L.nQ : L.nK;
+    const int32_t* lo = plan + (is_q ? L.off_kvlo : L.off_qlo) + bh * n;
+    const int32_t* hi = plan + (is_q ? L.off_kvhi : L.off_qhi) + bh * n;
+    int32_t* ord = plan + (is_q ? L.off_ordq : L.off_ordk) + bh * n;
+    // natural position i: query block nQ-1-i, key block i
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int blk = is_q ? n - 1 - i : i;
+        len[i] = hi[blk] - lo[blk];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int li = len[i];
+        int rank = 0;
+        for (int j = 0; j < n; ++j) rank += (len[j] > li) || (len[j] == li && j < i);
+        ord[rank] = is_q ? n - 1 - i : i;
+    }
+}
+
 // grid (nK, nQ, B*He), 128 threads: one tile. A tile that the plan does not visit reports
 // keep = 0 everywhere, a tile without a flagged check reports keep = 1 for the entries that
 // check covers: exactly what the attention kernels assume.
@@ -176,6 +203,7 @@ cudaError_t launch_plan_build(const void* eq_ptr, const int64_t* eq_stride, int 
     dim3 grid(L.nQ + L.nK, L.He, L.B);
     plan_codes_kernel<<<grid, 128, 0, stream>>>(q, k, plan, L, status);
     plan_ranges_kernel<<<grid, 128, 0, stream>>>(plan, L, gap, causal);
+    plan_order_kernel<<<dim3(2, L.He, L.B), 1024, 0, stream>>>(plan, L);
     return cudaGetLastError();
 }
 

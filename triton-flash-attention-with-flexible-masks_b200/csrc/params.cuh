@@ -6,13 +6,13 @@ namespace fa {
 
 constexpr int kAttnThreads = 384;  // 3 warpgroups: two compute groups, one producer / MMA group
 constexpr int kFwdThreads = kAttnThreads;
-constexpr int kListCap = 1024;     // blocks per sequence (visited-tile lists live in shared memory)
 
 struct FwdParams {
     float* lse;  // [B, H, Mpad], log2 domain
     MaskArgs mask;
     int H, B, G;
     int gh;            // heads per scheduling group
+    int by_length;     // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2;  // sm_scale * log2(e)
     int* status;
 };
@@ -31,6 +31,7 @@ struct DkdvParams {
     MaskArgs mask;
     int B, H, Hk, G;
     int gh;  // kv heads per scheduling group
+    int by_length;  // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2, sm_scale;
     int* status;
 };
@@ -41,6 +42,7 @@ struct DqParams {
     MaskArgs mask;
     int B, H, G;
     int gh;  // heads per scheduling group
+    int by_length;  // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2, sm_scale;
     int* status;
 };

@@ -141,7 +141,7 @@ def build_plan(prob, eq, ek, status):
                                      status.data_ptr(), _stream()), "fa_plan_build")
         return plan
     ieq, iek = _ids(eq), _ids(ek)
-    with _Timed("plan", 2):
+    with _Timed("plan", 3):
         _lib.check(lib.fa_plan_build(ctypes.byref(prob), ctypes.byref(ieq), ctypes.byref(iek), plan.data_ptr(),
                                      nbytes.value, status.data_ptr(), _stream()), "fa_plan_build")
     return plan
