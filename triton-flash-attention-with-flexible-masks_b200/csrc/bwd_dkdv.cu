@@ -19,9 +19,9 @@
 //   warp 10    tcgen05.mma issuer for dV, dK and dP^T
 //   warp 11    scheduler: per item, the range of candidate query blocks and their flags
 // The Q / dO rings and all per-tile barriers run across item boundaries, so the next item's K and
-// first Q / dO tiles are in flight and its first S^T is computed while the compute groups drain the
-// accumulators of the finished item (dV is staged in the P^T tile, dK in the V tile, both dead by
-// then; V of the next item is loaded when the stores have read them).
+// V and first Q / dO tiles are in flight and its first S^T is computed while the compute groups drain
+// the accumulators of the finished item (dK and dV are staged in the Q and dO ring stage of the
+// item's last tile, which is dead by then; that stage is refilled when the stores have read it).
 // TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [256+D,256+2D).
 #include "common.cuh"
 #include "params.cuh"
@@ -48,8 +48,8 @@ struct DkdvSmem {
     static constexpr int off_info = off_flags + 2 * FLAGS;  // two item slots x {lo, n, tiles, -}
     static constexpr int off_bar = off_info + 32;
     // k_full, v_full, k_empty, q_full[NST], do_full[NST], q_empty[NST], do_empty[NST], s_full, s_free,
-    // dp_full, p_full, p_free, ds_full, done, acc_free, staged, stage_free, item_full[2], item_empty[2]
-    static constexpr int n_bar = 3 + 4 * NST + 10 + 4;
+    // dp_full, p_full, p_free, ds_full, done, acc_free, staged, stage_free, item_full[2], item_empty[2], v_empty
+    static constexpr int n_bar = 3 + 4 * NST + 10 + 4 + 1;
     static constexpr int off_misc = off_bar + n_bar * 8;
     static constexpr int total = off_misc + 16;
 };
@@ -132,7 +132,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               B_DOEMPTY = B_QEMPTY + NST, B_SFULL = B_DOEMPTY + NST, B_SFREE = B_SFULL + 1, B_DPFULL = B_SFULL + 2,
               B_PFULL = B_SFULL + 3, B_PFREE = B_SFULL + 4, B_DSFULL = B_SFULL + 5, B_DONE = B_SFULL + 6,
               B_ACCFREE = B_SFULL + 7, B_STAGED = B_SFULL + 8, B_STAGEFREE = B_SFULL + 9, B_ITEMFULL = B_SFULL + 10,
-              B_ITEMEMPTY = B_ITEMFULL + 2;
+              B_ITEMEMPTY = B_ITEMFULL + 2, B_VEMPTY = B_ITEMEMPTY + 2;
     Abort ab{misc + 1, p.status};
 
     const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v, sP = sbase + S::off_p;
@@ -158,6 +158,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(BAR(B_ACCFREE), 256);
         mbar_init(BAR(B_STAGED), 256);
         mbar_init(BAR(B_STAGEFREE), 1);
+        mbar_init(BAR(B_VEMPTY), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(BAR(B_ITEMFULL + s), 1);
             mbar_init(BAR(B_ITEMEMPTY + s), 11);  // producer, two MMA issuers, eight compute warps
@@ -252,14 +253,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 int k = 0, kk = 0;  // items, items with tiles
                 int gt = 0;         // tiles of all earlier items (stage / phase of the Q and dO rings)
                 int pkb = 0, phk = 0, pb = 0;  // the previous item, whose dK / dV are still to be stored
-                // stores the staged dV (P^T tile) and dK (V tile) of item i and frees the staging tiles
-                auto finish_store = [&](int i, int kb, int hk, int b) {
+                // stores the dV / dK of item i, staged in the dO / Q ring stage `st`, and frees the stage
+                auto finish_store = [&](int i, int kb, int hk, int b, int st) {
                     bool o = mbar_wait(BAR(B_STAGED), i & 1, ab, ST_WAIT_TIMEOUT + 55);
                     if (!o) return false;
                     if (misc[1] == 0) {
                         for (int x = 0; x < S::NBOX; ++x) {
-                            tma_store_4d(&tmdV, sP + x * S::BOX, x * 64, kb * kBlk, hk, b);
-                            tma_store_4d(&tmdK, sV + x * S::BOX, x * 64, kb * kBlk, hk, b);
+                            tma_store_4d(&tmdV, sdO(st) + x * S::BOX, x * 64, kb * kBlk, hk, b);
+                            tma_store_4d(&tmdK, sQ(st) + x * S::BOX, x * 64, kb * kBlk, hk, b);
                         }
                         tma_store_commit();
                         tma_store_wait_read();
@@ -295,22 +296,24 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         wk.advance(cg, cc);
                         return true;
                     };
-                    const int npre = NIT < NST ? NIT : NST;
+                    // The previous item is staged in ring stage (gt + NST - 1) % NST, the stage of its last
+                    // tile. K, V and the tiles of the other stages do not wait for its epilogue.
+                    const int npre = NIT < NST - 1 ? NIT : NST - 1;
                     if (NIT > 0) {
-                        // K and the first Q / dO tiles do not wait for the previous item's epilogue
                         if (kk > 0) ok = mbar_wait(BAR(B_KEMPTY), (kk - 1) & 1, ab, ST_WAIT_TIMEOUT + 57);
                         if (!ok) break;
                         mbar_expect_tx(BAR(B_KFULL), S::TILE);
                         for (int x = 0; x < S::NBOX; ++x) tma_load_4d(sK + x * S::BOX, &tmK, BAR(B_KFULL), x * 64, kb * kBlk, hk, b);
+                        if (kk > 0) ok = mbar_wait(BAR(B_VEMPTY), (kk - 1) & 1, ab, ST_WAIT_TIMEOUT + 60);
+                        if (!ok) break;
+                        mbar_expect_tx(BAR(B_VFULL), S::TILE);
+                        for (int x = 0; x < S::NBOX; ++x) tma_load_4d(sV + x * S::BOX, &tmV, BAR(B_VFULL), x * 64, kb * kBlk, hk, b);
                         for (int it = 0; it < npre && ok; ++it) ok = load_qdo(it);
                         if (!ok) break;
                     }
-                    if (k > 0) ok = finish_store(k - 1, pkb, phk, pb);
+                    if (k > 0) ok = finish_store(k - 1, pkb, phk, pb, (gt + NST - 1) % NST);
                     if (!ok) break;
                     if (NIT > 0) {
-                        // the V tile was the dK staging area of the previous item
-                        mbar_expect_tx(BAR(B_VFULL), S::TILE);
-                        for (int x = 0; x < S::NBOX; ++x) tma_load_4d(sV + x * S::BOX, &tmV, BAR(B_VFULL), x * 64, kb * kBlk, hk, b);
                         for (int it = npre; it < NIT && ok; ++it) ok = load_qdo(it);
                         if (!ok) break;
                         ++kk;
@@ -319,7 +322,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     pkb = kb; phk = hk; pb = b;
                     mbar_arrive(BAR(B_ITEMEMPTY + s));
                 }
-                if (ok && k > 0) finish_store(k - 1, pkb, phk, pb);
+                if (ok && k > 0) finish_store(k - 1, pkb, phk, pb, (gt + NST - 1) % NST);
             }
         } else {
             // ------------------------------ MMA issuers (warps 9, 10) ------------------------------
@@ -372,6 +375,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         tc_fence_after();
                         ss_mmas(tmem + 128u, sV, sdO(gt % NST));  // dP^T(0)
                         umma_commit(BAR(B_DPFULL));
+                        if (NIT == 1) umma_commit(BAR(B_VEMPTY));  // V may be replaced after the item's last dP^T
                         // dV(0) and dK(0) overwrite the accumulators: the previous item's epilogue must have read them
                         if (kk > 0) ok = mbar_wait(BAR(B_ACCFREE), (kk - 1) & 1, ab, ST_WAIT_TIMEOUT + 58);
                         for (int it = 0; it < NIT && ok; ++it) {
@@ -404,6 +408,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             if (more) {
                                 ss_mmas(tmem + 128u, sV, sdO((gi + 1) % NST));  // dP^T(it+1)
                                 umma_commit(BAR(B_DPFULL));
+                                if (it + 2 == NIT) umma_commit(BAR(B_VEMPTY));
                             }
                         }
                         if (!ok) break;
@@ -536,10 +541,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                 }
                 // P^T (input dtype) -> shared memory, K-major 128-byte-swizzled rows: this thread's 64
-                // queries are one 128-byte row of box `w`. The previous tile's dV MMAs must have read the
-                // tile, and (first tile of an item) the previous item's dV, staged in it, must have left.
+                // queries are one 128-byte row of box `w`. The previous tile's dV MMAs must have read the tile.
                 if (gi > 0) ok = mbar_wait(BAR(B_PFREE), (gi - 1) & 1, ab, ST_WAIT_TIMEOUT + 51);
-                if (ok && it == 0 && k > 0) ok = mbar_wait(BAR(B_STAGEFREE), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 59);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 {
@@ -590,25 +593,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!ok) break;
 
             // ------------------------------ item epilogue ------------------------------
-            if (NIT > 0) {
-                ok = mbar_wait(BAR(B_DONE), kk & 1, ab, ST_WAIT_TIMEOUT + 51);
-            } else if (k > 0) {
-                ok = mbar_wait(BAR(B_STAGEFREE), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 59);  // the staging tiles are free
-            }
+            if (NIT > 0) ok = mbar_wait(BAR(B_DONE), kk & 1, ab, ST_WAIT_TIMEOUT + 51);
+            // the previous item's stores have read their staging stage (it may be the same one)
+            if (ok && k > 0) ok = mbar_wait(BAR(B_STAGEFREE), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 59);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             if (r == 0) FA_TRACE_EV(w, 44);
             {
                 // dV and dK * sm_scale (flash_triton.py:313) go out through shared memory: each thread
-                // writes its half rows into the (now dead) P^T and V tiles in the tensor maps'
-                // 128-byte-swizzled layout; the producer warp issues the TMA stores, which clip rows >= N.
+                // writes its half rows into the dO and Q ring stage of the item's last tile (dead: all MMAs
+                // of the item are complete) in the tensor maps' 128-byte-swizzled layout; the producer warp
+                // issues the TMA stores, which clip rows >= N.
+                const int sst = (gt + NIT + NST - 1) % NST;
                 constexpr int HALF = D / 2;
                 const uint32_t c0 = uint32_t(w) * HALF;
 #pragma unroll
                 for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
                     const float mul = which ? p.sm_scale : 1.0f;
-                    uint8_t* stage = smem + (which ? S::off_v : S::off_p);
+                    uint8_t* stage = smem + (which ? S::off_q : S::off_do) + sst * S::TILE;
 #pragma unroll
                     for (int q = 0; q < HALF / 32; ++q) {
                         uint32_t x[32];
