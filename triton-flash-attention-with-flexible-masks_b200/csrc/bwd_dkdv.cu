@@ -45,8 +45,8 @@ struct DkdvSmem {
     static constexpr int off_p = off_do + NST * TILE;
     static constexpr int off_vec = off_p + PT;
     static constexpr int off_flags = off_vec + NST * VEC;  // two item slots
-    static constexpr int off_info = off_flags + 2 * FLAGS;  // two item slots x {lo, n, tiles, -}
-    static constexpr int off_bar = off_info + 32;
+    static constexpr int off_info = off_flags + 2 * FLAGS;  // two item slots x {lo, n, tiles, item, key block, kv head, batch, -}
+    static constexpr int off_bar = off_info + 64;
     // k_full, v_full, k_empty, q_full[NST], do_full[NST], q_empty[NST], do_empty[NST], s_full, s_free,
     // dp_full, p_full, p_free, ds_full, done, acc_free, staged, stage_free, item_full[2], item_empty[2], v_empty
     static constexpr int n_bar = 3 + 4 * NST + 10 + 4 + 1;
@@ -200,7 +200,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 j = __shfl_sync(0xffffffffu, j, 0);
                 if (j >= n_items) {  // end marker
                     if (lane == 0) {
-                        info[s * 4 + 3] = -1;
+                        info[s * 8 + 3] = -1;
                         mbar_arrive(BAR(B_ITEMFULL + s));
                     }
                     break;
@@ -237,10 +237,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
                 __syncwarp();
                 if (lane == 0) {
-                    info[s * 4 + 0] = lo;
-                    info[s * 4 + 1] = n;
-                    info[s * 4 + 2] = cnt * G;  // tiles of all query heads of the group, head-major
-                    info[s * 4 + 3] = j;
+                    info[s * 8 + 0] = lo;
+                    info[s * 8 + 1] = n;
+                    info[s * 8 + 2] = cnt * G;  // tiles of all query heads of the group, head-major
+                    info[s * 8 + 3] = j;
+                    info[s * 8 + 4] = kb;
+                    info[s * 8 + 5] = hk;
+                    info[s * 8 + 6] = b;
                     mbar_arrive(BAR(B_ITEMFULL + s));
                 }
             }
@@ -272,10 +275,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const int s = k & 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 56);
                     if (!ok) break;
-                    const int lo = info[s * 4 + 0], n = info[s * 4 + 1], NIT = info[s * 4 + 2], j = info[s * 4 + 3];
+                    const int lo = info[s * 8 + 0], n = info[s * 8 + 1], NIT = info[s * 8 + 2], j = info[s * 8 + 3];
                     if (j < 0) break;
-                    int kb, hk, b;
-                    decode(j, kb, hk, b);
+                    const int kb = info[s * 8 + 4], hk = info[s * 8 + 5], b = info[s * 8 + 6];
                     const Walk wk = walk_of(s, n);
                     int cg = 0, cc = wk.first_from(0);
                     auto load_qdo = [&](int it) {
@@ -350,8 +352,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const int s = k & 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 56);
                     if (!ok) break;
-                    const int NIT = info[s * 4 + 2];
-                    if (info[s * 4 + 3] < 0) break;
+                    const int NIT = info[s * 8 + 2];
+                    if (info[s * 8 + 3] < 0) break;
                     if (NIT > 0 && warp == 9) {
                         ok = mbar_wait(BAR(B_KFULL), kk & 1, ab, ST_WAIT_TIMEOUT + 43);
                         for (int it = 0; it < NIT && ok; ++it) {
@@ -438,10 +440,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 56);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const int lo = info[s * 4 + 0], n = info[s * 4 + 1], NIT = info[s * 4 + 2], jt = info[s * 4 + 3];
+            const int lo = info[s * 8 + 0], n = info[s * 8 + 1], NIT = info[s * 8 + 2], jt = info[s * 8 + 3];
             if (jt < 0) break;
-            int kb, hk, b;
-            decode(jt, kb, hk, b);
+            const int kb = info[s * 8 + 4], hk = info[s * 8 + 5], b = info[s * 8 + 6];
             const Walk wk = walk_of(s, n);
             const int j = kb * kBlk + r;  // this thread's key
             const int k0 = kb * kBlk, k1 = min(k0 + kBlk, mk.N);
@@ -593,9 +594,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!ok) break;
 
             // ------------------------------ item epilogue ------------------------------
-            if (NIT > 0) ok = mbar_wait(BAR(B_DONE), kk & 1, ab, ST_WAIT_TIMEOUT + 51);
             // the previous item's stores have read their staging stage (it may be the same one)
-            if (ok && k > 0) ok = mbar_wait(BAR(B_STAGEFREE), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 59);
+            if (k > 0) ok = mbar_wait(BAR(B_STAGEFREE), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 59);
+            // dV is final (and the last dO tile dead) when the last dV MMAs are complete: it is drained
+            // while the last dK MMAs still run
+            if (ok && NIT > 0) ok = mbar_wait(BAR(B_PFREE), (gt + NIT - 1) & 1, ab, ST_WAIT_TIMEOUT + 51);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -610,6 +613,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const uint32_t c0 = uint32_t(w) * HALF;
 #pragma unroll
                 for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
+                    if (which == 1 && NIT > 0) {
+                        ok = mbar_wait(BAR(B_DONE), kk & 1, ab, ST_WAIT_TIMEOUT + 51);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
                     const float mul = which ? p.sm_scale : 1.0f;
                     uint8_t* stage = smem + (which ? S::off_q : S::off_do) + sst * S::TILE;
 #pragma unroll
@@ -635,6 +644,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     }
                 }
             }
+            if (!ok) break;
             // both accumulators have been read: warp 10 may start the next item's dV / dK
             tc_fence_before();
             if (NIT > 0) {

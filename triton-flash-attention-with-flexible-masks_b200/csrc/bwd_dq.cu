@@ -35,8 +35,8 @@ struct DqSmem {
     static constexpr int off_k = 4 * TILE;
     static constexpr int off_vec = off_k + NSK * TILE;  // two slots
     static constexpr int off_flags = off_vec + 2 * VEC;  // two slots
-    static constexpr int off_info = off_flags + 2 * FLAGS;  // two slots x {lo, n, tiles, item}
-    static constexpr int off_bar = off_info + 32;
+    static constexpr int off_info = off_flags + 2 * FLAGS;  // two slots x {lo, n, tiles, item, query block, head, batch, -}
+    static constexpr int off_bar = off_info + 64;
     // item_full[2], item_empty[2], q_full[2], staged[2], do_full, do_empty, v_full, v_empty, k_full[NSK],
     // k_empty[NSK], s_full[2], ds_full[2], dp_full, done, acc_free
     static constexpr int n_bar = 8 + 4 + 2 * NSK + 4 + 3;
@@ -159,7 +159,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 j = __shfl_sync(0xffffffffu, j, 0);
                 if (j >= n_items) {
                     if (lane == 0) {
-                        info[s * 4 + 3] = -1;
+                        info[s * 8 + 3] = -1;
                         mbar_arrive(BAR(B_ITEMFULL + s));
                     }
                     break;
@@ -188,10 +188,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
                 __syncwarp();
                 if (lane == 0) {
-                    info[s * 4 + 0] = lo;
-                    info[s * 4 + 1] = n;
-                    info[s * 4 + 2] = cnt;
-                    info[s * 4 + 3] = j;
+                    info[s * 8 + 0] = lo;
+                    info[s * 8 + 1] = n;
+                    info[s * 8 + 2] = cnt;
+                    info[s * 8 + 3] = j;
+                    info[s * 8 + 4] = qb;
+                    info[s * 8 + 5] = h;
+                    info[s * 8 + 6] = b;
                     mbar_arrive(BAR(B_ITEMFULL + s));
                 }
             }
@@ -203,14 +206,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 bool ok = true;
                 int k = 0, kk = 0;  // items, items with tiles
                 int gt = 0;         // tiles of all earlier items (stage / phase of the K ring and of V)
-                int item_of[2] = {0, 0};  // the items in the two slots
+                int item_qb[2] = {0, 0}, item_h[2] = {0, 0}, item_b[2] = {0, 0};  // the items in the two slots
                 // TMA store of the dQ tile the compute groups staged in slot (i & 1) for item i
                 auto store_dq = [&](int i) {
                     const int s = i & 1;
                     if (!mbar_wait(BAR(B_STAGED + s), (i >> 1) & 1, ab, ST_WAIT_TIMEOUT + 32)) return false;
                     if (misc[1] == 0) {
-                        int qb, h, b;
-                        decode(item_of[s], qb, h, b);
+                        const int qb = item_qb[s], h = item_h[s], b = item_b[s];
                         for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmdQ, sQ(s) + x * S::BOX, x * 64, qb * kBlk, h, b);
                         tma_store_commit();
                         tma_store_wait_read();
@@ -221,15 +223,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     const int s = k & 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 33);
                     if (!ok) break;
-                    const int lo = info[s * 4 + 0], n = info[s * 4 + 1], T = info[s * 4 + 2], j = info[s * 4 + 3];
+                    const int lo = info[s * 8 + 0], n = info[s * 8 + 1], T = info[s * 8 + 2], j = info[s * 8 + 3];
                     if (j < 0) break;
-                    int qb, h, b;
-                    decode(j, qb, h, b);
+                    const int qb = info[s * 8 + 4], h = info[s * 8 + 5], b = info[s * 8 + 6];
                     const int hk = h / p.G;
                     // the slot still holds the staged dQ tile of item k-2: send it off first
                     if (k >= 2) ok = store_dq(k - 2);
                     if (!ok) break;
-                    item_of[s] = j;
+                    item_qb[s] = qb; item_h[s] = h; item_b[s] = b;
                     // Q with the rows' LSE and delta (also for an item without tiles: its dQ = 0 is staged in the slot)
                     mbar_expect_tx(BAR(B_QFULL + s), S::TILE + S::VEC);
                     for (int x = 0; x < S::NBOX; ++x)
@@ -305,8 +306,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     const int s = k & 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 33);
                     if (!ok) break;
-                    const int T = info[s * 4 + 2];
-                    if (info[s * 4 + 3] < 0) break;
+                    const int T = info[s * 8 + 2];
+                    if (info[s * 8 + 3] < 0) break;
                     if (T > 0 && warp == 9) {
                         ok = mbar_wait(BAR(B_QFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 23);
                         const uint32_t q_tile = sQ(s);
@@ -387,10 +388,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             ok = mbar_wait(BAR(B_ITEMFULL + s), (k >> 1) & 1, ab, ST_WAIT_TIMEOUT + 33);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const int lo = info[s * 4 + 0], n = info[s * 4 + 1], T = info[s * 4 + 2], j = info[s * 4 + 3];
+            const int lo = info[s * 8 + 0], n = info[s * 8 + 1], T = info[s * 8 + 2], j = info[s * 8 + 3];
             if (j < 0) break;
-            int qb, h, b;
-            decode(j, qb, h, b);
+            const int qb = info[s * 8 + 4], h = info[s * 8 + 5], b = info[s * 8 + 6];
             const int he = (mk.He == 1) ? 0 : h;
             const DqWalk wk = walk_of(s, n);
             const int row = qb * kBlk + r;

@@ -44,8 +44,8 @@ struct FwdSmem {
     static constexpr int off_qc = off_list + 2 * kListCap * 2;  // int32  [2][128] query codes
     static constexpr int off_kc = off_qc + 2 * kBlk * 4;        // int32  [NKC][128] key codes, loaded with K
     static constexpr int off_ml = off_kc + NKC * kBlk * 4;      // float  [2][2 groups][m, l][128]
-    static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][4]: T, lo, item (-1: no more items)
-    static constexpr int off_bar = off_info + 32;
+    static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][8]: T, lo, item (-1: no more items), -, query block, head, batch
+    static constexpr int off_bar = off_info + 64;
     // item_full[2] item_empty[2] q_full[2] o_staged[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
     // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] kc_full[NKC] ml_full
     static constexpr int n_bar = 8 + 4 * NS + 12 + 8 + 1;
@@ -156,7 +156,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 j = __shfl_sync(0xffffffffu, j, 0);
                 if (j >= n_items) {  // end marker
                     if (lane == 0) {
-                        info[s * 4 + 2] = -1;
+                        info[s * 8 + 2] = -1;
                         mbar_arrive(BAR(B_ITEMFULL + s));
                     }
                     break;
@@ -183,9 +183,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                                                          int64_t(qb) * kBlk + lane * 4);
                 reinterpret_cast<int4*>(smem + S::off_qc)[s * 32 + lane] = qc4;
                 if (lane == 0) {
-                    info[s * 4 + 0] = T;
-                    info[s * 4 + 1] = lo;
-                    info[s * 4 + 2] = j;
+                    info[s * 8 + 0] = T;
+                    info[s * 8 + 1] = lo;
+                    info[s * 8 + 2] = j;
+                    info[s * 8 + 4] = qb;
+                    info[s * 8 + 5] = h;
+                    info[s * 8 + 6] = b;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR(B_ITEMFULL + s));
@@ -199,12 +202,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 bool ok = true;
                 int k = 0, G = 0;  // G: tiles of all earlier items (the K / V rings run across items)
                 // TMA store of the O tile the softmax groups staged in slot (kk & 1) for item kk
-                int item_of[2] = {0, 0};  // the items in the two slots
+                int item_qb[2] = {0, 0}, item_h[2] = {0, 0}, item_b[2] = {0, 0};  // the items in the two slots
                 auto store_o = [&](int kk) {
                     const int s = kk & 1;
                     if (!mbar_wait(BAR(B_OSTAGED + s), (kk >> 1) & 1, ab, ST_WAIT_TIMEOUT + 13)) return false;
-                    int qb, h, b;
-                    decode(item_of[s], qb, h, b);
+                    const int qb = item_qb[s], h = item_h[s], b = item_b[s];
                     for (int x = 0; x < S::NBOX; ++x) tma_store_4d(&tmO, sQ(s) + x * S::BOX, x * 64, qb * kBlk, h, b);
                     tma_store_commit();
                     tma_store_wait_read();
@@ -214,17 +216,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     const int s = k & 1, use = k >> 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
                     if (!ok) break;
-                    const int T = info[s * 4 + 0], lo = info[s * 4 + 1], j = info[s * 4 + 2];
+                    const int T = info[s * 8 + 0], lo = info[s * 8 + 1], j = info[s * 8 + 2];
                     if (j < 0) break;
                     const uint16_t* list = list_of(s);
-                    int qb, h, b;
-                    decode(j, qb, h, b);
+                    const int qb = info[s * 8 + 4], h = info[s * 8 + 5], b = info[s * 8 + 6];
                     const int hk = h / p.G;
                     const int he = (mk.He == 1) ? 0 : h;
                     // the slot still holds the staged O tile of item k-2: send it off first
                     if (use > 0) ok = store_o(k - 2);
                     if (!ok) break;
-                    item_of[s] = j;
+                    item_qb[s] = qb; item_h[s] = h; item_b[s] = b;
                     mbar_expect_tx(BAR(B_QFULL + s), S::TILE);
                     for (int x = 0; x < S::NBOX; ++x)
                         tma_load_4d(sQ(s) + x * S::BOX, &tmQ, BAR(B_QFULL + s), x * 64, qb * kBlk, h, b);
@@ -288,8 +289,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     const int s = k & 1, use = k >> 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
                     if (!ok) break;
-                    const int T = info[s * 4 + 0];
-                    if (info[s * 4 + 2] < 0) break;
+                    const int T = info[s * 8 + 0];
+                    if (info[s * 8 + 2] < 0) break;
                     ok = mbar_wait(BAR(B_QFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 3);
                     if (!ok) break;
                     const uint32_t q_tile = sQ(s);
@@ -370,14 +371,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             alive = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
-            const int T = info[s * 4 + 0];
-            const int lo = info[s * 4 + 1];
-            const int j = info[s * 4 + 2];
+            const int T = info[s * 8 + 0];
+            const int lo = info[s * 8 + 1];
+            const int j = info[s * 8 + 2];
             if (j < 0) break;
             if (r == 0) FA_TRACE_EV(w, 32 + (T > 63 ? 63 : T));
             const uint16_t* list = list_of(s);
-            int qb, h, b;
-            decode(j, qb, h, b);
+            const int qb = info[s * 8 + 4], h = info[s * 8 + 5], b = info[s * 8 + 6];
             const int row = qb * kBlk + r;
             const int qc = reinterpret_cast<const int*>(smem + S::off_qc)[s * kBlk + r];
             float m_run = -INFINITY, l_run = 0.f;
