@@ -135,3 +135,15 @@ def test_shard_slices():
     assert dim == 1 and qs == slice(8, 16) and ks == slice(2, 4)
     with pytest.raises(ValueError):
         shard.shard_slices(3, 3, 3, 2, 0)
+
+
+def test_host_slices_cover_everything_once():
+    """attention_host cuts [B, H] into independent slices: batches when B > 1, else groups of kv heads."""
+    from flash_b200.host import _slices
+    dim, sl = _slices(1, 32, 8, 8)
+    assert dim == 1 and len(sl) == 8
+    assert [s[:2] for s in sl] == [(4 * i, 4 * i + 4) for i in range(8)] and [s[2:] for s in sl] == [(i, i + 1) for i in range(8)]
+    dim, sl = _slices(1, 6, 3, 8)  # fewer kv heads than parts
+    assert dim == 1 and [s[2:] for s in sl] == [(0, 1), (1, 2), (2, 3)] and sl[-1][:2] == (4, 6)
+    dim, sl = _slices(5, 4, 4, 2)
+    assert dim == 0 and sl[0][0] == 0 and sl[-1][1] == 5 and all(a[1] == b[0] for a, b in zip(sl, sl[1:]))

@@ -81,3 +81,27 @@ def test_fixed_order_without_plan_matches_counters(monkeypatch, causal):
     for a, b in zip(with_counters, without_plan):
         assert torch.isfinite(a.float()).all()
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("B,H,Hk,mode", [(1, 8, 4, 1), (3, 4, 4, 1), (1, 4, 4, 0)])
+def test_attention_host_matches_attention(B, H, Hk, mode):
+    """The streamed call for host tensors computes slices of heads (or batches) on their own: same bits."""
+    import flash_b200 as fb
+    dev = torch.device("cuda", 0)
+    L, D = 640, 64
+    g = torch.Generator().manual_seed(13)
+    q = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16).pin_memory()
+    k, v = [torch.randn(B, Hk, L, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    do = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16).pin_memory()
+    ids = torch.from_numpy(_doc_ids(L, [100, 333]))[None, None, :].repeat(B, 1, 1) if mode == 1 else None
+    res = fb.attention_host(q, k, v, do, True, 0.125, ids, ids, mode, parts=3, device=dev)
+    torch.cuda.synchronize()
+    fb.check_status()
+    qd, kd, vd = [t.to(dev).requires_grad_() for t in (q, k, v)]
+    idd = ids.to(dev).expand(B, H, L) if ids is not None else None
+    o = fb.attention(qd, kd, vd, True, 0.125, idd, idd, mode)
+    o.backward(do.to(dev))
+    torch.cuda.synchronize()
+    for name, ref in (("o", o.detach()), ("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
+        assert torch.isfinite(res[name].float()).all()
+        assert torch.equal(res[name], ref.cpu()), name
