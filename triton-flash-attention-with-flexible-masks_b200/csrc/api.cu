@@ -227,7 +227,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     fp.B = p->B;
     fp.G = p->H / p->Hk;
     fp.gh = head_group(p, p->H * p->B);
-    fp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 64 * int64_t(sms)) ? 1 : 0;
+    fp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 32 * int64_t(sms)) ? 1 : 0;
     fp.scale_log2 = p->sm_scale * kLog2e;
     fp.status = status;
     const cudaError_t e =
@@ -283,7 +283,7 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     kp.Hk = p->Hk;
     kp.G = p->H / p->Hk;
     kp.gh = head_group(p, p->Hk * p->B);
-    kp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->N, fa::kBlk) * p->Hk * p->B) < 64 * int64_t(sms)) ? 1 : 0;
+    kp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->N, fa::kBlk) * p->Hk * p->B) < 32 * int64_t(sms)) ? 1 : 0;
     kp.scale_log2 = p->sm_scale * kLog2e;
     kp.sm_scale = p->sm_scale;
     kp.status = status;
@@ -321,7 +321,7 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     qp.H = p->H;
     qp.G = p->H / p->Hk;
     qp.gh = head_group(p, p->H * p->B);
-    qp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 64 * int64_t(sms)) ? 1 : 0;
+    qp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 32 * int64_t(sms)) ? 1 : 0;
     qp.scale_log2 = p->sm_scale * kLog2e;
     qp.sm_scale = p->sm_scale;
     qp.status = status;
