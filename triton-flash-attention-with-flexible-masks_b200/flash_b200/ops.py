@@ -258,7 +258,19 @@ class FlashAttention(torch.autograd.Function):
 
 
 def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
-    """Drop-in for flash_triton.py:640-641."""
+    """Drop-in for flash_triton.py:640-641.
+
+    The kernels are built for head dims 64 and 128. The reference's smaller head dims (16 and 32,
+    flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
+    nothing to q k^T, produce zero output columns, and their gradient columns are cut off again
+    (autograd differentiates the padding and the slice)."""
+    D = q.shape[-1]
+    if D in (16, 32) and k.shape[-1] == D and v.shape[-1] == D:
+        if sm_scale is None:
+            sm_scale = 1. / math.sqrt(D)  # of the true head dim (flash_triton.py:523)
+        pad = (0, 64 - D)
+        q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+        return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)[..., :D]
     return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
 
 
