@@ -336,6 +336,34 @@ def test_small_head_dims_through_padding(fb, D):
     fb.check_status()
 
 
+@pytest.mark.parametrize("per_head", [False, True])
+def test_query_gather_for_ungrouped_ids(fb, per_head):
+    """Random query ids, no causal mask (the layout of configuration 2): with GATHER_QUERIES the
+    queries are sorted by id for the kernels and the results come back in the caller's order."""
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    B, H, Hk, M, N, D = 2, 4, 2, 700, 1024, 64
+    q = torch.randn(B, H, M, D, generator=g).mul(0.5).to("cuda", torch.float16).requires_grad_()
+    k = torch.randn(B, Hk, N, D, generator=g).mul(0.5).to("cuda", torch.float16).requires_grad_()
+    v = torch.randn(B, Hk, N, D, generator=g).mul(0.5).to("cuda", torch.float16).requires_grad_()
+    do = torch.randn(B, H, M, D, generator=g).to("cuda", torch.float16)
+    He = H if per_head else 1
+    eq = -(torch.randint(0, 4, (B, He, M), generator=g) + 1)
+    eq[:, :, ::37] = 3  # some positions that attend to everything
+    ek = -(torch.arange(N) // (N // 4) + 1)[None, None, :].expand(B, He, N).contiguous()
+    eq, ek = eq.to("cuda").expand(B, H, M), ek.to("cuda").expand(B, H, N)
+    ops.GATHER_QUERIES = True
+    try:
+        o = fb.attention(q, k, v, False, None, eq, ek, 1)
+        o.backward(do)
+    finally:
+        ops.GATHER_QUERIES = False
+    ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(),
+                                                       False, None, eq.cpu(), ek.cpu(), 1)
+    close(o, ro, "O"); close(q.grad, rdq, "dQ"); close(k.grad, rdk, "dK"); close(v.grad, rdv, "dV")
+    fb.check_status()
+
+
 def test_unsupported_inputs_raise(fb):
     x = torch.zeros(1, 1, 64, 48, dtype=BF, device="cuda")
     with pytest.raises(AssertionError):  # the reference's own check on the head dim (flash_triton.py:512)

@@ -257,8 +257,36 @@ class FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+# Without a causal mask the order of the queries is free. When the query ids are not grouped (every
+# block of 128 queries holds every document) no tile can be skipped and every tile needs the id check;
+# with GATHER_QUERIES = True the queries of such calls are first sorted by id (a stable sort: grouped
+# ids stay as they are), which makes the blocks (nearly) uniform again, and the results are put back
+# in the caller's order. Off by default: it costs a gather of q and a scatter of o / dq per call.
+GATHER_QUERIES = False
+
+
+def _attention_gathered(q, k, v, sm_scale, eq, ek):
+    B, H, M, D = q.shape
+    eq = _id_tensor(eq, B, H, M, "eq")
+    shared = (H == 1) or eq.stride(1) == 0  # one id row per batch, broadcast over the heads
+    rows = eq[:, :1] if shared else eq
+    perm = torch.argsort(rows, dim=-1, stable=True)                      # [B, 1|H, M]
+    inv = torch.empty_like(perm).scatter_(-1, perm, torch.arange(M, device=q.device).expand_as(perm))
+    eq_s = torch.gather(rows, -1, perm).expand(B, H, M)
+    idx = perm.expand(B, H, M)[..., None].expand(B, H, M, D)
+    o_s = attention_ungathered(torch.gather(q, 2, idx), k, v, False, sm_scale, eq_s, ek, SCORE_FUNC_MODE1_DOC)
+    return torch.gather(o_s, 2, inv.expand(B, H, M)[..., None].expand(B, H, M, D))
+
+
 def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
-    """Drop-in for flash_triton.py:640-641.
+    """Drop-in for flash_triton.py:640-641."""
+    if GATHER_QUERIES and score_func_mode == SCORE_FUNC_MODE1_DOC and not causal and eq is not None and q.is_cuda:
+        return _attention_gathered(q, k, v, sm_scale, eq, ek)
+    return attention_ungathered(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
+
+
+def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
+    """`attention` with the queries in the caller's order.
 
     The kernels are built for head dims 64 and 128. The reference's smaller head dims (16 and 32,
     flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
