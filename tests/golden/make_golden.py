@@ -1,8 +1,8 @@
 """Generates the golden fixtures of this directory from the REFERENCE ITSELF.
 
-Run in a container that has the reference checkout (default /root/reference, or $FA_REFERENCE):
+Run where the reference checkout is available, with its directory in $FA_REFERENCE:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py
+    FA_REFERENCE=<reference checkout> TRITON_INTERPRET=1 python tests/golden/make_golden.py
 
 For every case it stores the seeded inputs and the outputs of
   * the reference's torch masked-attention path `_attn_torch` (testing.py:32-47), fp32, with
@@ -20,7 +20,9 @@ import sys
 os.environ.setdefault("TRITON_INTERPRET", "1")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, ".."))
-REF = os.environ.get("FA_REFERENCE", "/root/reference")
+REF = os.environ.get("FA_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set FA_REFERENCE to the directory of the reference checkout")
 sys.path.insert(0, REF)
 
 import numpy as np
