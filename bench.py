@@ -225,25 +225,76 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    # The timed step is one CUDA graph of the step's calls (plan, forward, backward): a rank's share of
+    # the step is short (0.5 ms at 8 GPUs) and Python enqueues it more slowly than the GPU runs it when
+    # the host is busy, which a graph replay does not depend on. With one rank the per-kernel events
+    # are captured into the timed graph as event-record nodes and read after the last timed replay.
+    # They cost about 4 us each, too much for the short steps of several ranks: there the timed graph
+    # has none and the per-kernel times come from one replay of a second graph (with the events) right
+    # after the timed region. --no-graph times plain eager calls (every step carries its own events).
+    use_graph = not args.no_graph
     for _ in range(args.warmup):
+        flush.zero_()
         step()
+    barrier()
+    graph = None
+    launches_per_step = 0
+    prof_graph = None
+    if use_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph_prof = torch.cuda.CUDAGraph()
+            ops.PROFILE = []
+            l0 = ops.LAUNCHES
+            with torch.cuda.graph(graph_prof):
+                step()
+            launches_per_step = ops.LAUNCHES - l0
+            prof_graph, ops.PROFILE = ops.PROFILE, None
+            graph = graph_prof
+            if world > 1:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+            graph.replay()
+            torch.cuda.synchronize()
+            fb.check_status()
+        except Exception as exc:  # capture refused: time eager steps instead
+            print(f"[bench] CUDA graph capture failed ({exc}); timing eager steps", file=sys.stderr)
+            graph, ops.PROFILE = None, None
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    ops.PROFILE = []
+    if graph is None:
+        ops.PROFILE = []
     launches0 = ops.LAUNCHES
     evs = []
     for _ in range(args.steps):
         flush.zero_()  # L2 flush between timed iterations (not timed)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        step()
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
         e1.record()
         evs.append((e0, e1))
     barrier()
     clocks = sampler.stop()
-    prof, ops.PROFILE = ops.PROFILE, None
-    launches = ops.LAUNCHES - launches0
+    if graph is None:
+        prof, ops.PROFILE = ops.PROFILE, None
+        launches = ops.LAUNCHES - launches0
+    else:
+        if graph is not graph_prof:  # several ranks: one replay of the graph that holds the per-kernel events
+            flush.zero_()
+            graph_prof.replay()
+            torch.cuda.synchronize()
+        prof = prof_graph  # as recorded by the last replay of the graph that holds them
+        launches = launches_per_step * args.steps
     fb.check_status()
     total_ms = sum(a.elapsed_time(b) for a, b in evs)
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -330,6 +381,11 @@ def run_ours(args):
                 "config": {"workload": workload_name(name, cfg), "seed": workloads.SEEDS[name],
                            "sharding": f"{'heads' if dim == 1 else 'batches'} over {world} rank(s), {n_local} per rank",
                            "l2": "256 MiB buffer written between timed iterations",
+                           "timed_step": ("eager calls with per-kernel events" if graph is None else
+                                          "one CUDA graph replay per step (plan, forward, backward); per-kernel events are nodes of "
+                                          "the graph, read after the last timed replay" if world == 1 else
+                                          "one CUDA graph replay per step (plan, forward, backward); per-kernel times from one replay "
+                                          "of the same step with event nodes, right after the timed region"),
                            "unmasked_fraction_of_causal": nnz_total / dense,
                            "dense_count_tflops": (14.0 if backward else 4.0) * D * dense / (ms_per_step * 1e-3) / 1e12},
                 "frac_of_measured_peak": value / (peak_tf * world), "frac_of_nominal_peak": value / (2250.0 * world),
@@ -350,6 +406,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (small profiling cases)")
     ap.add_argument("--heads", type=int, default=None, help="override the head count (small profiling cases)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time eager calls instead of CUDA-graph replays of the step")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -36,8 +36,11 @@ class _Timed:
         global LAUNCHES
         LAUNCHES += self.kernels
         if PROFILE is not None:
-            self.e0 = torch.cuda.Event(enable_timing=True)
-            self.e1 = torch.cuda.Event(enable_timing=True)
+            # inside a CUDA graph capture the events become record nodes of the graph, re-recorded by
+            # every replay and readable after it
+            ext = torch.cuda.is_current_stream_capturing()
+            self.e0 = torch.cuda.Event(enable_timing=True, external=ext)
+            self.e1 = torch.cuda.Event(enable_timing=True, external=ext)
             self.e0.record()
         return self
 
