@@ -130,6 +130,10 @@ def test_parity_with_always_attend_positions(fb):
 def test_parity_per_head_ids_with_grouped_heads(fb):
     run_case(fb, 1, 4, 2, 512, 512, 64, True, 1, BF, ndoc=4, per_head=True)
     run_case(fb, 2, 6, 2, 384, 384, 128, False, 1, FP, ndoc=5, per_head=True, seed=3)
+    # heads of one group whose blocks differ in being monotone (always-attend positions break it for some
+    # heads only): the chunk shortcuts of the id check must then be off for the whole group
+    run_case(fb, 2, 8, 4, 1500, 1500, 64, False, 1, FP, ndoc=4, pos_frac=0.03, per_head=True, seed=28)
+    run_case(fb, 1, 8, 2, 1024, 1024, 128, True, 1, BF, ndoc=6, pos_frac=0.02, per_head=True, seed=5)
 
 
 def test_parity_int32_ids(fb):

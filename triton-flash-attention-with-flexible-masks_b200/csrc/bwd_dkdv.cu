@@ -61,16 +61,20 @@ static_assert(DkdvSmem<128>::total <= 232448 && DkdvSmem<64>::total <= 232448, "
 enum : uint32_t { KC_SKIP = 0u, KC_PLAIN = 1u, KC_DOC = 2u, KC_DOCMONO = 3u };
 
 // Flags of tile (qb, kb) for all query heads of one kv head at once. When the heads disagree
-// (ids given per head) the id check is forced, which is always exact.
+// (ids given per head) the id check is forced, entry by entry, which is always exact.
 __device__ __forceinline__ uint32_t classify_group(const MaskArgs& mk, int b, int hk, int G, int qb, int kb) {
     if (mk.He == 1 || G == 1) return classify_from_plan(mk, b, mk.He == 1 ? 0 : hk * G, qb, kb);
-    uint32_t f = 0;
+    uint32_t f = 0, mono = TILE_KMONO | TILE_QMONO;
     bool all = true;
     for (int g = 0; g < G; ++g) {
         const uint32_t fg = classify_from_plan(mk, b, hk * G + g, qb, kb);
-        if (fg & TILE_VISIT) f |= fg; else all = false;
+        if (fg & TILE_VISIT) { f |= fg; mono &= fg; } else all = false;
     }
+    // the chunk shortcuts of the id check may only be taken if the codes are monotone for every head
+    // that the check is applied to (a head that reports no id check does not report its monotony)
+    f &= ~(TILE_KMONO | TILE_QMONO);
     if (f && !all) f |= TILE_DOC;
+    else f |= mono;
     return f;
 }
 
