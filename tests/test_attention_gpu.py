@@ -136,6 +136,31 @@ def test_parity_per_head_ids_with_grouped_heads(fb):
     run_case(fb, 1, 8, 2, 1024, 1024, 128, True, 1, BF, ndoc=6, pos_frac=0.02, per_head=True, seed=5)
 
 
+def test_ragged_last_block_that_starts_with_an_always_attend_position(fb):
+    """Last (ragged) block = [id >= 0, then one document]: its valid codes are monotone, but together with the
+    padding codes the block is not, and a 32-entry chunk whose two ends are padding / always-attend codes is
+    not uniform. Key side (forward, dQ) and query side (dK/dV)."""
+    B, H, Hk, M, N, D = 1, 2, 1, 200, 405, 128
+    g = torch.Generator().manual_seed(98)
+    q = torch.randn(B, H, M, D, generator=g).to("cuda", FP).requires_grad_()
+    k = torch.randn(B, Hk, N, D, generator=g).to("cuda", FP).requires_grad_()
+    v = torch.randn(B, Hk, N, D, generator=g).to("cuda", FP).requires_grad_()
+    do = torch.randn(B, H, M, D, generator=g).to("cuda", FP)
+    ek = torch.full((N,), -1, dtype=torch.int64)
+    ek[300:] = -4
+    ek[384] = 7          # first key of the last block attends / is attended like an id >= 0
+    eq = torch.full((M,), -1, dtype=torch.int64)
+    eq[100:] = -4
+    eq[128] = 7          # first query of the last block
+    eqd, ekd = eq.to("cuda")[None, None].expand(B, H, M), ek.to("cuda")[None, None].expand(B, H, N)
+    o = fb.attention(q, k, v, False, None, eqd, ekd, 1)
+    o.backward(do)
+    ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(),
+                                                       False, None, eqd.cpu(), ekd.cpu(), 1)
+    close(o, ro, "O"); close(q.grad, rdq, "dQ"); close(k.grad, rdk, "dK"); close(v.grad, rdv, "dV")
+    fb.check_status()
+
+
 def test_parity_int32_ids(fb):
     run_case(fb, 1, 2, 2, 512, 512, 128, True, 1, BF, ndoc=4, id_dtype=torch.int32)
 

@@ -26,8 +26,9 @@ __host__ __device__ inline int64_t pad128(int64_t x) { return (x + 127) / 128 * 
 //   kmin, kmax [B, He, nK]   min / max key code per block of 128 keys
 //   kv_lo, kv_hi [B, He, nQ] range of key blocks with an unmasked entry, per query block
 //   q_lo, q_hi   [B, He, nK] range of query blocks with an unmasked entry, per key block
-//   qmono [B, He, nQ], kmono [B, He, nK]  1 if the codes of the block are monotone (non-decreasing or
-//                non-increasing), i.e. equal codes are adjacent: the usual packed-documents layout
+//   qmono [B, He, nQ], kmono [B, He, nK]  1 if the codes of the block (all 128 stored codes, padding of a
+//                ragged last block included) are monotone (non-decreasing or non-increasing), i.e. equal
+//                codes are adjacent: the usual packed-documents layout
 //   ord_q [B, He, nQ], ord_k [B, He, nK]  the blocks of a head sorted by the length of their visit range,
 //                longest first (ties: from the long end of a causal head)
 //   ctr [128]    work counters of the persistent kernels (item counter, finished-CTA counter per kernel);

@@ -74,12 +74,13 @@ __global__ void __launch_bounds__(128) plan_codes_kernel(IdsView eq, IdsView ek,
     if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) plan[L.off_ctr + threadIdx.x] = 0;
     const int mn = block_reduce_min(valid ? code : 0x7fffffff, scratch);
     const int mx = block_reduce_max(valid ? code : int(-2147483647 - 1), scratch);
-    // monotone within the block (valid entries): no rise or no fall between neighbours
+    // monotone within the block: no rise or no fall between neighbours. The padding entries of a ragged
+    // last block count too (with the codes stored for them): the kernels' chunk tests read them.
     __shared__ int codes[kBlk];
     codes[threadIdx.x] = code;
     __syncthreads();
     int rise = 0, fall = 0;
-    if (valid && threadIdx.x > 0) {
+    if (threadIdx.x > 0) {
         rise = code > codes[threadIdx.x - 1];
         fall = code < codes[threadIdx.x - 1];
     }
