@@ -228,7 +228,7 @@ def run_ours(args):
     # The timed step is one CUDA graph of the step's calls (plan, forward, backward): a rank's share of
     # the step is short (0.5 ms at 8 GPUs) and Python enqueues it more slowly than the GPU runs it when
     # the host is busy, which a graph replay does not depend on. With one rank the per-kernel events
-    # are captured into the timed graph as event-record nodes and read after the last timed replay.
+    # are captured into the timed graph as event-record nodes and read after every timed replay.
     # They cost about 4 us each, too much for the short steps of several ranks: there the timed graph
     # has none and the per-kernel times come from one replay of a second graph (with the events) right
     # after the timed region. --no-graph times plain eager calls (every step carries its own events).
@@ -273,6 +273,7 @@ def run_ours(args):
         ops.PROFILE = []
     launches0 = ops.LAUNCHES
     evs = []
+    kern_acc = {}
     for _ in range(args.steps):
         flush.zero_()  # L2 flush between timed iterations (not timed)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -283,6 +284,11 @@ def run_ours(args):
             step()
         e1.record()
         evs.append((e0, e1))
+        if graph is not None and graph is graph_prof:
+            # the graph's event nodes are re-recorded by every replay: read this step's kernel times now
+            torch.cuda.synchronize()
+            for nm, a, c in prof_graph:
+                kern_acc.setdefault(nm, []).append(a.elapsed_time(c))
     barrier()
     clocks = sampler.stop()
     if graph is None:
@@ -305,9 +311,10 @@ def run_ours(args):
     value = flops_step_total / (ms_per_step * 1e-3) / 1e12
 
     # per-kernel durations measured live in the timed region (events on the launching stream)
-    kern = {}
-    for nm, a, b in prof:
-        kern.setdefault(nm, []).append(a.elapsed_time(b))
+    kern = kern_acc
+    if not kern:
+        for nm, a, b in prof:
+            kern.setdefault(nm, []).append(a.elapsed_time(b))
     kern_ms = {nm: float(np.mean(x)) for nm, x in kern.items()}
     peak_tf, peak_bw, peak_src = peaks()
     dom = max((nm for nm in kern_ms if nm in FLOPS_PER_ENTRY), key=lambda nm: kern_ms[nm])
@@ -383,7 +390,7 @@ def run_ours(args):
                            "l2": "256 MiB buffer written between timed iterations",
                            "timed_step": ("eager calls with per-kernel events" if graph is None else
                                           "one CUDA graph replay per step (plan, forward, backward); per-kernel events are nodes of "
-                                          "the graph, read after the last timed replay" if world == 1 else
+                                          "the graph, read after every timed replay" if world == 1 else
                                           "one CUDA graph replay per step (plan, forward, backward); per-kernel times from one replay "
                                           "of the same step with event nodes, right after the timed region"),
                            "unmasked_fraction_of_causal": nnz_total / dense,
