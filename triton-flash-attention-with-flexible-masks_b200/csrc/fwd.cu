@@ -285,6 +285,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 const uint32_t tO = tmem + 256u + uint32_t(w) * uint32_t(D);
                 bool ok = true;
                 int k = 0, G = 0, cw = 0;  // cw: tiles this chain has finished (phases of its barriers)
+                int kkw = 0;               // items in which this chain had tiles (phase of its o_free barrier)
                 for (;; ++k) {
                     const int s = k & 1, use = k >> 1;
                     ok = mbar_wait(BAR(B_ITEMFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 12);
@@ -322,8 +323,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         FA_TRACE_EV(2 + w, 20);
                         if (ok && more) ok = k_ready(g + 2);
                         FA_TRACE_EV(2 + w, 21);
-                        // the first P*V of an item overwrites O: the previous item's epilogue must have read it
-                        if (ok && i == 0 && k > 0) ok = mbar_wait(BAR(B_OFREE + w), (k - 1) & 1, ab, ST_WAIT_TIMEOUT + 14);
+                        // The first P*V of an item overwrites O: the epilogue of the previous item in which this
+                        // chain had tiles must have read it. (The barrier counts those items only, on both
+                        // sides: a chain without tiles in an item runs through it and must not find itself two
+                        // phases behind, where a parity wait can no longer tell "not yet" from "done".)
+                        if (ok && i == 0 && kkw > 0) ok = mbar_wait(BAR(B_OFREE + w), (kkw - 1) & 1, ab, ST_WAIT_TIMEOUT + 14);
                         if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
                         if (!ok) break;
                         tc_fence_after();
@@ -346,6 +350,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         FA_TRACE_EV(2 + w, 25);
                     }
                     G += T;
+                    if (nmine > 0) ++kkw;
                     if (ok) mbar_arrive(BAR(B_ITEMEMPTY + s));
                 }
             }
@@ -548,6 +553,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             // wait for this group's last P*V, then merge the two partial softmaxes
             if (r == 0) FA_TRACE_EV(w, 1);
             if (!alive) break;
+            if (T == 0) {
+                // nobody has waited for this item's Q load yet, and its slot is about to become the staging
+                // area of the (all-zero) output tile: the load must have landed first
+                alive = mbar_wait(BAR(B_QFULL + s), use & 1, ab, ST_WAIT_TIMEOUT + 17);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+            }
             if (n_my > 0) {
                 alive = mbar_wait(BAR(B_PVDONE + w), (cw - 1) & 1, ab, ST_WAIT_TIMEOUT + 9);
                 alive = __all_sync(0xffffffffu, alive);
@@ -605,10 +617,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             }
             // both accumulators have been read: the MMA issuers may start the next item's P*V
             tc_fence_before();
-            if (alive) {
-                mbar_arrive(BAR(B_OFREE + 0));
-                mbar_arrive(BAR(B_OFREE + 1));
-            }
+            if (T > 0) mbar_arrive(BAR(B_OFREE + 0));  // group 0 had tiles
+            if (T > 1) mbar_arrive(BAR(B_OFREE + 1));  // group 1 had tiles
             // Stage the O tile in this item's Q slot (Q is dead: every S MMA of the item has
             // completed) in the 128-byte-swizzled layout of the tensor map; the producer warp issues
             // the TMA store when every thread has arrived, and reuses the slot once it has been read.
