@@ -5,7 +5,7 @@
 // (flash_triton.py:88), and tiles the mask plan proves empty are not visited at all.
 //
 // Persistent: one CTA per SM walks work items (one item = one block of 128 queries of one
-// (batch, head)); item j of CTA c is c + j * gridDim.x in an order that puts the query blocks of
+// (batch, head)); items are handed out in an order that puts the query blocks of
 // all heads side by side, so that the CTAs of one round carry almost equal work. With document
 // masks most items hold only a few tiles, so everything around the tiles is overlapped with the
 // neighbouring items: a scheduler warp prepares the next item's tile list, the producer prefetches
@@ -17,9 +17,12 @@
 //   warps 9,10 tcgen05.mma issuers, one per softmax group; warp 9 owns the TMEM allocation
 //   warp 11    item scheduler: decodes the item, classifies its candidate tiles from the mask plan
 //              and compacts the visited ones into a list in shared memory (two item slots)
-// Visited key tiles of an item alternate between the two groups: tile t uses score buffer S[t&1]
-// and accumulates into O[t&1] with its own running max / sum; the two partial results are merged
-// in the item's epilogue. TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+// Visited key tiles alternate between the two groups: the CTA's g-th tile (counted across its items)
+// uses score buffer S[g&1] and accumulates into O[g&1] with the group's own running max / sum for
+// the item; the two partial results are merged in the item's epilogue, the chain of the item's even
+// tiles first, so that the result does not depend on which group that was. Counting across items
+// keeps every K / V ring slot (slot g % NS, NS even) with one issuer, which waits for each of
+// its phases in turn, and lets consecutive one-tile items overlap on the two chains. TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (input dtype, two values per column) overwrites the first 64 columns of its S buffer.
 #include <type_traits>
 #include "common.cuh"
@@ -270,7 +273,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             }
         } else {
             // ------------------------------ MMA issuers ------------------------------
-            // One issuing thread per softmax group: warp 9 owns the even visited tiles (S0 / O0),
+            // One issuing thread per softmax group: warp 9 owns the CTA's even visited tiles (S0 / O0),
             // warp 10 the odd ones (S1 / O1). The two chains touch disjoint TMEM and only share the
             // K / V rings, so neither thread ever waits on the other group's softmax. Within a
             // chain the MMAs of P*V(t) and S(t+2) are issued back to back (the tensor pipe accepts
@@ -309,15 +312,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         umma_commit(BAR(B_KEMPTY + st));
                         umma_commit(BAR(B_SFULL + w));
                     };
-                    const int nmine = (T > w) ? (T - w + 1) / 2 : 0;
+                    const int t0 = (G ^ w) & 1;  // this chain's first tile of the item: G + t0 has parity w
+                    const int nmine = (T > t0) ? (T - t0 + 1) / 2 : 0;
                     if (nmine > 0) {
-                        ok = k_ready(G + w);
+                        ok = k_ready(G + t0);
                         if (!ok) break;
                         tc_fence_after();
-                        s_mmas(G + w);
+                        s_mmas(G + t0);
                     }
                     for (int i = 0; i < nmine && ok; ++i, ++cw) {
-                        const int g = G + w + 2 * i, st = g % NS;
+                        const int g = G + t0 + 2 * i, st = g % NS;
                         const bool more = i + 1 < nmine;
                         ok = mbar_wait(BAR(B_VFULL + st), (g / NS) & 1, ab, ST_WAIT_TIMEOUT + 5);
                         FA_TRACE_EV(2 + w, 20);
@@ -387,12 +391,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const int qc = reinterpret_cast<const int*>(smem + S::off_qc)[s * kBlk + r];
             float m_run = -INFINITY, l_run = 0.f;
             int n_my = 0;
-            const int n_other = (w == 0) ? T / 2 : (T + 1) / 2;  // tiles of the other group
+            const int we = G & 1;   // the group that owns the item's even tiles
+            const int t0 = w ^ we;  // this group's first tile of the item
+            const int n_other = (t0 == 0) ? T / 2 : (T + 1) / 2;  // tiles of the other group
             // short items: both groups simply run side by side; long items: the exp phase is taken in turns
             const bool turns = T >= kTurnMinTiles;
-            if (turns && w == 1 && alive) mbar_arrive(BAR(B_TURN + 0));  // group 0 takes the first turn
+            if (turns && t0 == 1 && alive) mbar_arrive(BAR(B_TURN + we));  // the owner of tile 0 takes the first turn
 
-            for (int t = w; t < T && alive; t += 2, ++n_my, ++cw) {
+            for (int t = t0; t < T && alive; t += 2, ++n_my, ++cw) {
                 const uint32_t entry = list[t];
                 const uint32_t fl = entry >> 10;
                 const int k0 = (lo + int(entry & 1023u)) * kBlk;
@@ -507,7 +513,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 // k-steps of P*V can start while the second half is still being exponentiated.
                 const uint64_t c2 = pack_f2(c, c), mneg2 = pack_f2(mneg, mneg);
                 uint64_t lacc0 = pack_f2(0.f, 0.f), lacc1 = lacc0;
-                // The exp phase is taken in turns (barriers turn[0], turn[1]; group 0 first): left alone,
+                // The exp phase is taken in turns (barriers turn[0], turn[1]; the owner of tile 0 first): left alone,
                 // the groups fall into lockstep, exponentiate together at half MUFU rate each and then
                 // queue their MMAs together, which halves the use of both pipes. In turns, one group
                 // exponentiates while the other group's P*V and next S run on the tensor pipe.
@@ -540,7 +546,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 exp_half(0);
                 exp_half(1);
                 // hand the turn over, unless the other group has no tile left to take it for
-                if (turns && (w == 0 ? (n_my < n_other) : (n_my + 1 < n_other))) mbar_arrive(BAR(B_TURN + (w ^ 1)));
+                if (turns && (t0 == 0 ? (n_my < n_other) : (n_my + 1 < n_other))) mbar_arrive(BAR(B_TURN + (w ^ 1)));
                 {
                     float a0, a1, b0, b1;
                     unpack_f2(lacc0, a0, a1);
@@ -576,8 +582,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (!alive) break;
             tc_fence_after();
             if (r == 0) FA_TRACE_EV(w, 3);
-            const float m0 = ml[0 * kBlk + r], l0 = ml[1 * kBlk + r];
-            const float m1 = ml[2 * kBlk + r], l1 = ml[3 * kBlk + r];
+            // index 0: the chain of the item's even tiles, 1: of its odd tiles
+            const float m0 = ml[(we * 2 + 0) * kBlk + r], l0 = ml[(we * 2 + 1) * kBlk + r];
+            const float m1 = ml[((we ^ 1) * 2 + 0) * kBlk + r], l1 = ml[((we ^ 1) * 2 + 1) * kBlk + r];
             const float mt = fmaxf(m0, m1);
             const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2((m0 - mt) * c);
             const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2((m1 - mt) * c);
@@ -590,7 +597,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 const float lse = (lt > 0.f) ? fmaf(mt, c, log2f(lt)) : -INFINITY;
                 p.lse[(int64_t(b) * p.H + h) * mk.L.Mpad + row] = lse;
             }
-            // this thread's half row: O0 and O1 columns [w*D/2, (w+1)*D/2)
+            // this thread's half row: columns [w*D/2, (w+1)*D/2) of both accumulators
             constexpr int HALF = D / 2;
             const uint32_t c0 = uint32_t(w) * HALF;
             uint32_t outw[HALF / 2];
@@ -598,8 +605,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             for (int q = 0; q < HALF / 32; ++q) {
                 uint32_t x0[32], x1[32];
                 // tcgen05.ld is warp-collective: always executed, the values are ignored when unused
-                tmem_ld32(tmem + lane_base + 256u + c0 + uint32_t(q) * 32u, x0);
-                tmem_ld32(tmem + lane_base + 256u + uint32_t(D) + c0 + uint32_t(q) * 32u, x1);
+                tmem_ld32(tmem + lane_base + 256u + uint32_t(we * D) + c0 + uint32_t(q) * 32u, x0);
+                tmem_ld32(tmem + lane_base + 256u + uint32_t((we ^ 1) * D) + c0 + uint32_t(q) * 32u, x1);
                 tc_wait_ld();
 #pragma unroll
                 for (int x = 0; x < 16; ++x) {
@@ -617,8 +624,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             }
             // both accumulators have been read: the MMA issuers may start the next item's P*V
             tc_fence_before();
-            if (T > 0) mbar_arrive(BAR(B_OFREE + 0));  // group 0 had tiles
-            if (T > 1) mbar_arrive(BAR(B_OFREE + 1));  // group 1 had tiles
+            if (T > 0) mbar_arrive(BAR(B_OFREE + we));        // the chain of the even tiles had some
+            if (T > 1) mbar_arrive(BAR(B_OFREE + (we ^ 1)));  // so had the other chain
             // Stage the O tile in this item's Q slot (Q is dead: every S MMA of the item has
             // completed) in the 128-byte-swizzled layout of the tensor map; the producer warp issues
             // the TMA store when every thread has arrived, and reuses the slot once it has been read.
