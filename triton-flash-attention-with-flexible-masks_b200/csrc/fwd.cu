@@ -45,13 +45,13 @@ struct FwdSmem {
     static constexpr int off_v = off_k + NS * TILE;
     static constexpr int off_list = off_v + NS * TILE;         // uint16 [2][kListCap]
     static constexpr int off_qc = off_list + 2 * kListCap * 2;  // int32  [2][128] query codes
-    static constexpr int off_kc = off_qc + 2 * kBlk * 4;        // int32  [NKC][128] key codes, loaded with K
+    static constexpr int off_kc = off_qc + 2 * kBlk * 4;        // int32  [NKC][128] key codes, loaded with K on K's barrier
     static constexpr int off_ml = off_kc + NKC * kBlk * 4;      // float  [2][2 groups][m, l][128]
     static constexpr int off_info = off_ml + 2 * 2 * 2 * kBlk * 4;  // int32 [2][8]: T, lo, item (-1: no more items), -, query block, head, batch
     static constexpr int off_bar = off_info + 64;
     // item_full[2] item_empty[2] q_full[2] o_staged[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
-    // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] kc_full[NKC] ml_full
-    static constexpr int n_bar = 8 + 4 * NS + 12 + 8 + 1;
+    // s_full[2] p_half0[2] p_half1[2] pv_done[2] turn[2] o_free[2] ml_full
+    static constexpr int n_bar = 8 + 4 * NS + 12 + 1;
     static constexpr int off_misc = off_bar + n_bar * 8;  // tmem slot, abort flag
     static constexpr int total = off_misc + 16;
 };
@@ -79,8 +79,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto BAR = [&](int i) { return bar0 + 8u * uint32_t(i); };
     constexpr int B_ITEMFULL = 0, B_ITEMEMPTY = 2, B_QFULL = 4, B_OSTAGED = 6, B_KFULL = 8, B_KEMPTY = 8 + NS,
                   B_VFULL = 8 + 2 * NS, B_VEMPTY = 8 + 3 * NS, B_SFULL = 8 + 4 * NS, B_PHALF0 = B_SFULL + 2,
-                  B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_KCFULL = B_SFULL + 12,
-                  B_MLFULL = B_KCFULL + S::NKC;
+                  B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_MLFULL = B_SFULL + 12;
     Abort ab{misc + 1, p.status};
 
     if (tid == 0) {
@@ -96,7 +95,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             mbar_init(BAR(B_TURN + s), 128);
             mbar_init(BAR(B_OFREE + s), 256);
         }
-        for (int s = 0; s < S::NKC; ++s) mbar_init(BAR(B_KCFULL + s), 1);
         mbar_init(BAR(B_MLFULL), 256);
         for (int s = 0; s < NS; ++s) {
             mbar_init(BAR(B_KFULL + s), 1);
@@ -239,18 +237,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                             if (ug > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 1);
                             if (!ok) break;
                             FA_TRACE_EV(4, 30);
-                            // The tile's key codes are fetched with K into a ring of NKC slots (own barriers). Slot g % NKC was
-                            // last read by the softmax of tile g - NKC, which is over: this thread has
-                            // already waited for the P*V of tile g - 2 - NS before issuing V(g - 2).
-                            mbar_expect_tx(BAR(B_KFULL + st), S::TILE);
+                            // The tile's key codes travel with K: they land in a ring of NKC slots and complete on
+                            // K's barrier, so whoever has seen S(g) (computed after that barrier) may read them.
+                            // Slot g % NKC was last read by the softmax of tile g - NKC, which is over: this thread
+                            // has already waited for the P*V of tile g - 2 - NS before issuing V(g - 2).
+                            mbar_expect_tx(BAR(B_KFULL + st), S::TILE + (mk.mode == 1 ? kBlk * 4 : 0));
                             for (int x = 0; x < S::NBOX; ++x)
                                 tma_load_4d(sK(st) + x * S::BOX, &tmK, BAR(B_KFULL + st), x * 64, kb * kBlk, hk, b);
-                            if (mk.mode == 1) {
-                                mbar_expect_tx(BAR(B_KCFULL + g % S::NKC), kBlk * 4);
+                            if (mk.mode == 1)
                                 bulk_load_1d(sbase + S::off_kc + (g % S::NKC) * (kBlk * 4),
                                              mk.plan + mk.L.off_kc + (int64_t(b) * mk.He + he) * mk.L.Npad + int64_t(kb) * kBlk,
-                                             kBlk * 4, BAR(B_KCFULL + g % S::NKC));
-                            }
+                                             kBlk * 4, BAR(B_KFULL + st));
                         }
                         if (t >= 1) {
                             const int kb = lo + (list[t - 1] & 1023);
@@ -427,12 +424,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     }
                     const bool doc = (fl & TILE_DOC) && qc < 0;  // a row with qc >= 0 passes the id check everywhere
                     const int* kcs = reinterpret_cast<const int*>(smem + S::off_kc + ((G + t) % S::NKC) * (kBlk * 4));
-                    if (fl & TILE_DOC) {  // the key codes were fetched together with the K tile
-                        const int g = G + t;
-                        alive = mbar_wait(BAR(B_KCFULL + g % S::NKC), (g / S::NKC) & 1, ab, ST_WAIT_TIMEOUT + 15);
-                        alive = __all_sync(0xffffffffu, alive);
-                        if (!alive) break;
-                    }
+                    // (the key codes completed on K's barrier, before the S MMA whose result was just read)
                     if (r == 0) FA_TRACE_EV(w, 11);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
