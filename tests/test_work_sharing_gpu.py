@@ -94,7 +94,8 @@ def test_attention_host_matches_attention(B, H, Hk, mode):
     k, v = [torch.randn(B, Hk, L, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(2)]
     do = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16).pin_memory()
     ids = torch.from_numpy(_doc_ids(L, [100, 333]))[None, None, :].repeat(B, 1, 1) if mode == 1 else None
-    res = fb.attention_host(q, k, v, do, True, 0.125, ids, ids, mode, parts=3, device=dev)
+    # the device defaults to the current one
+    res = fb.attention_host(q, k, v, do, True, 0.125, ids, ids, mode, parts=3, **({} if mode == 0 else {"device": dev}))
     torch.cuda.synchronize()
     fb.check_status()
     qd, kd, vd = [t.to(dev).requires_grad_() for t in (q, k, v)]

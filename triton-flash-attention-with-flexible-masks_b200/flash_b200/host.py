@@ -45,7 +45,7 @@ def attention_host(q, k, v, do=None, causal=False, sm_scale=None, eq=None, ek=No
     CPU tensors "o", "dq", "dk", "dv" to receive the results (allocated if missing).
     Returns the dict. The copies and kernels are enqueued on three streams; the current stream
     waits for all of them at the end, so events recorded on it bracket the whole call."""
-    dev = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     B, H, M, D = q.shape
     Hk = k.shape[1]
     backward = do is not None
