@@ -27,6 +27,10 @@ def _side_streams(dev):
 
 # slices the copy-in stream may be ahead of the kernels (0: no limit)
 _LOOKAHEAD = int(os.environ.get("FA_B200_HOST_LOOKAHEAD", "2"))
+# slices the calling thread may enqueue ahead of the kernels before it blocks (0: no limit)
+_HOST_AHEAD = int(os.environ.get("FA_B200_HOST_AHEAD", "0"))
+# 1: return only when the results are in host memory
+_HOST_SYNC = os.environ.get("FA_B200_HOST_SYNC", "0") not in ("", "0")
 
 
 class _Ctx:
@@ -87,6 +91,8 @@ def attention_host(q, k, v, do=None, causal=False, sm_scale=None, eq=None, ek=No
 
         finished = []  # per slice: the event after its kernels
         for (qa, qb, ka, kb) in slices:
+            if 0 < _HOST_AHEAD <= len(finished):
+                finished[-_HOST_AHEAD].synchronize()
             with torch.cuda.stream(s_in):
                 # The copy-in stream runs at most _LOOKAHEAD slices ahead of the kernels. Left alone it queues
                 # all copies back to back, and the kernels of a slice, which wait for that slice's copies,
@@ -137,4 +143,6 @@ def attention_host(q, k, v, do=None, causal=False, sm_scale=None, eq=None, ek=No
                     cut(out[name], lo, hi).copy_(t, non_blocking=True)
         for s in (s_in, s_cmp, s_out):
             cur.wait_stream(s)
+        if _HOST_SYNC:
+            cur.synchronize()
     return out
