@@ -147,3 +147,16 @@ def test_host_slices_cover_everything_once():
     assert dim == 1 and [s[2:] for s in sl] == [(0, 1), (1, 2), (2, 3)] and sl[-1][:2] == (4, 6)
     dim, sl = _slices(5, 4, 4, 2)
     assert dim == 0 and sl[0][0] == 0 and sl[-1][1] == 5 and all(a[1] == b[0] for a, b in zip(sl, sl[1:]))
+
+
+def test_cpulist_parser_and_numa_binding_without_gpu():
+    """sysfs cpulist format; without a GPU (or without the sysfs entries) the binding changes nothing."""
+    import os
+    from flash_b200 import host
+    assert host._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert host._parse_cpulist("5") == {5}
+    assert host._parse_cpulist("") == set()
+    before = os.sched_getaffinity(0)
+    if not torch.cuda.is_available():
+        assert host.bind_to_gpu_numa_node("cuda:0") is None
+        assert os.sched_getaffinity(0) == before
