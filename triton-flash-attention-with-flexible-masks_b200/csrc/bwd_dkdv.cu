@@ -25,7 +25,6 @@
 // TMEM columns: S^T [0,128)  dP^T [128,256)  dV [256,256+D)  dK [256+D,256+2D).
 #include "common.cuh"
 #include "params.cuh"
-#include "trace.cuh"
 
 namespace fa {
 
@@ -105,7 +104,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int G = p.G;
@@ -370,7 +368,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             ss_mmas(tmem, sK, sQ(st));
                             umma_commit(BAR(B_QEMPTY + st));
                             umma_commit(BAR(B_SFULL));
-                            FA_TRACE_EV(2, 2);
                         }
                         if (!ok) break;
                         umma_commit(BAR(B_KEMPTY));
@@ -450,7 +447,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const Walk wk = walk_of(s, n);
             const int j = kb * kBlk + r;  // this thread's key
             const int k0 = kb * kBlk, k1 = min(k0 + kBlk, mk.N);
-            if (r == 0) FA_TRACE_EV(w, 40);
 
             int cg = 0, cc = wk.first_from(0);
             int kc = 0, kc_g = -1;  // this key's code for the current query head
@@ -465,7 +461,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const float* vlse = reinterpret_cast<const float*>(smem + S::off_vec + st * S::VEC) + cbase;
                 const float* vdelta = vlse + kBlk;
 
-                if (r == 0) FA_TRACE_EV(w, 10);
                 ok = mbar_wait(BAR(B_QFULL + st), (gi / NST) & 1, ab, ST_WAIT_TIMEOUT + 49);
                 if (ok) ok = mbar_wait(BAR(B_SFULL), gi & 1, ab, ST_WAIT_TIMEOUT + 50);
                 ok = __all_sync(0xffffffffu, ok);
@@ -477,7 +472,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tc_wait_ld();
                 tc_fence_before();
                 mbar_arrive(BAR(B_SFREE));  // the next S^T may now overwrite the columns
-                if (r == 0) FA_TRACE_EV(w, 12);
                 float* pr = reinterpret_cast<float*>(sr);
                 {
                     // P^T = exp2(S^T*c - LSE) on packed pairs. A fully masked row has LSE = -inf and only
@@ -564,13 +558,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
                 fence_proxy_async();
                 mbar_arrive(BAR(B_PFULL));
-                if (r == 0) FA_TRACE_EV(w, 15);
 
                 ok = mbar_wait(BAR(B_DPFULL), gi & 1, ab, ST_WAIT_TIMEOUT + 52);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (r == 0) FA_TRACE_EV(w, 16);
                 uint32_t pk[32];
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
@@ -593,7 +585,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(B_DSFULL));
-                if (r == 0) FA_TRACE_EV(w, 17);
             }
             if (!ok) break;
 
@@ -606,7 +597,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (r == 0) FA_TRACE_EV(w, 44);
             {
                 // dV and dK * sm_scale (flash_triton.py:313) go out through shared memory: each thread
                 // writes its half rows into the dO and Q ring stage of the item's last tile (dead: all MMAs
@@ -660,7 +650,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             gt += NIT;
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(B_ITEMEMPTY + s));
-            if (r == 0) FA_TRACE_EV(w, 45);
         }
     }
 
@@ -695,7 +684,6 @@ static cudaError_t launch_dkdv_t(const CUtensorMap& tq, const CUtensorMap& tk, c
     return cudaGetLastError();
 }
 
-FA_TRACE_DUMP_FN(fa_trace_dump_dkdv)
 
 cudaError_t launch_bwd_dkdv(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const CUtensorMap& tdo, const CUtensorMap& tdk, const CUtensorMap& tdv,

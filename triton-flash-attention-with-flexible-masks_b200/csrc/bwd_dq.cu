@@ -17,7 +17,6 @@
 // written over the first half of each group's own S columns and fed to the dQ MMA from TMEM.
 #include "common.cuh"
 #include "params.cuh"
-#include "trace.cuh"
 
 namespace fa {
 
@@ -70,7 +69,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int nQ = mk.L.nQ;
@@ -324,11 +322,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         if (ok && kk > 0) ok = mbar_wait(BAR(B_ACCFREE), (kk - 1) & 1, ab, ST_WAIT_TIMEOUT + 35);
                         for (int t = 0; t < T && ok; ++t) {
                             const int gi = gt + t, st = gi % NSK;
-                            FA_TRACE_EV(2, 3);
                             ok = mbar_wait(BAR(B_DSFULL + (gi & 1)), (gi >> 1) & 1, ab, ST_WAIT_TIMEOUT + 26);
                             if (!ok) break;
                             tc_fence_after();
-                            FA_TRACE_EV(2, 4);
                             const uint32_t a = tmem + uint32_t(gi & 1) * 128u;
 #pragma unroll
                             for (int kk2 = 0; kk2 < kBlk / 16; ++kk2) {
@@ -346,7 +342,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                     umma_commit(BAR(B_SFULL + (gi & 1)));
                                 }
                             }
-                            FA_TRACE_EV(2, 5);
                         }
                         if (!ok) break;
                         umma_commit(BAR(B_DONE));
@@ -413,7 +408,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const bool fl_bound = (kb0 + kBlk > mk.N) || (mk.causal && kb1 - 1 > q0 + mk.gap);
                 const int k0 = kb0 + cbase;  // first key column of this thread
                 const uint32_t tS = tmem + lane_base + uint32_t(gi & 1) * 128u + uint32_t(cbase);
-                if (r == 0) FA_TRACE_EV(w, 10);
                 ok = mbar_wait(BAR(B_SFULL + (gi & 1)), (gi >> 1) & 1, ab, ST_WAIT_TIMEOUT + 27);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -423,7 +417,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld32(tS + 32u, sr + 32);
                 tc_wait_ld();
                 float* pr = reinterpret_cast<float*>(sr);
-                if (r == 0) FA_TRACE_EV(w, 12);
                 {
                     // P = exp2(S*c - LSE) on packed pairs
                     const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(-lse, -lse);
@@ -457,12 +450,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                         for (int x = 0; x < 64; ++x) pr[x] = (x <= lim) ? pr[x] : 0.f;
                     }
                 }
-                if (r == 0) FA_TRACE_EV(w, 13);
                 ok = mbar_wait(BAR(B_DPFULL), gi & 1, ab, ST_WAIT_TIMEOUT + 28);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (r == 0) FA_TRACE_EV(w, 16);
                 uint32_t pk[32];
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
@@ -485,7 +476,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(B_DSFULL + (gi & 1)));
-                if (r == 0) FA_TRACE_EV(w, 17);
             }
             if (!ok) break;
 
@@ -570,7 +560,6 @@ static cudaError_t launch_dq_t(const CUtensorMap& tq, const CUtensorMap& tk, con
     return cudaGetLastError();
 }
 
-FA_TRACE_DUMP_FN(fa_trace_dump_dq)
 
 cudaError_t launch_bwd_dq(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const CUtensorMap& tdo, const CUtensorMap& tdq, const DqParams& p, int num_sms, cudaStream_t stream) {

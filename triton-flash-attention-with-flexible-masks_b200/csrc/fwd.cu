@@ -27,7 +27,6 @@
 #include <type_traits>
 #include "common.cuh"
 #include "params.cuh"
-#include "trace.cuh"
 
 namespace fa {
 
@@ -65,7 +64,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    FA_TRACE_DECL
 
     const MaskArgs& mk = p.mask;
     const int nQ = mk.L.nQ;
@@ -236,7 +234,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                             const int g = G + t, st = g % NS, ug = g / NS;
                             if (ug > 0) ok = mbar_wait(BAR(B_KEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 1);
                             if (!ok) break;
-                            FA_TRACE_EV(4, 30);
                             // The tile's key codes travel with K: they land in a ring of NKC slots and complete on
                             // K's barrier, so whoever has seen S(g) (computed after that barrier) may read them.
                             // Slot g % NKC was last read by the softmax of tile g - NKC, which is over: this thread
@@ -254,7 +251,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                             const int g = G + t - 1, st = g % NS, ug = g / NS;
                             if (ug > 0) ok = mbar_wait(BAR(B_VEMPTY + st), (ug - 1) & 1, ab, ST_WAIT_TIMEOUT + 2);
                             if (!ok) break;
-                            FA_TRACE_EV(4, 31);
                             mbar_expect_tx(BAR(B_VFULL + st), S::TILE);
                             for (int x = 0; x < S::NBOX; ++x)
                                 tma_load_4d(sV(st) + x * S::BOX, &tmV, BAR(B_VFULL + st), x * 64, kb * kBlk, hk, b);
@@ -321,9 +317,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         const int g = G + t0 + 2 * i, st = g % NS;
                         const bool more = i + 1 < nmine;
                         ok = mbar_wait(BAR(B_VFULL + st), (g / NS) & 1, ab, ST_WAIT_TIMEOUT + 5);
-                        FA_TRACE_EV(2 + w, 20);
                         if (ok && more) ok = k_ready(g + 2);
-                        FA_TRACE_EV(2 + w, 21);
                         // The first P*V of an item overwrites O: the epilogue of the previous item in which this
                         // chain had tiles must have read it. (The barrier counts those items only, on both
                         // sides: a chain without tiles in an item runs through it and must not find itself two
@@ -332,23 +326,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         if (ok) ok = mbar_wait(BAR(B_PHALF0 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
                         if (!ok) break;
                         tc_fence_after();
-                        FA_TRACE_EV(2 + w, 22);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk)
                             umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv,
                                     (i > 0 || kk > 0) ? 1u : 0u);
-                        FA_TRACE_EV(2 + w, 23);
                         ok = mbar_wait(BAR(B_PHALF1 + w), cw & 1, ab, ST_WAIT_TIMEOUT + 6);
                         if (!ok) break;
                         tc_fence_after();
-                        FA_TRACE_EV(2 + w, 24);
 #pragma unroll
                         for (int kk = 4; kk < 8; ++kk)
                             umma_ts(tO, tS + uint32_t(kk) * 8u, smem_desc_at(desc_v, sV(st) + uint32_t(kk) * 2048u), idesc_pv, 1u);
                         umma_commit(BAR(B_VEMPTY + st));
                         umma_commit(BAR(B_PVDONE + w));
                         if (more) s_mmas(g + 2);
-                        FA_TRACE_EV(2 + w, 25);
                     }
                     G += T;
                     if (nmine > 0) ++kkw;
@@ -381,7 +371,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const int lo = info[s * 8 + 1];
             const int j = info[s * 8 + 2];
             if (j < 0) break;
-            if (r == 0) FA_TRACE_EV(w, 32 + (T > 63 ? 63 : T));
             const uint16_t* list = list_of(s);
             const int qb = info[s * 8 + 4], h = info[s * 8 + 5], b = info[s * 8 + 6];
             const int row = qb * kBlk + r;
@@ -403,13 +392,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 tc_fence_after();
-                if (r == 0) FA_TRACE_EV(w, 5);
                 uint32_t sr[128];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) tmem_ld32(tS + uint32_t(q) * 32u, sr + q * 32);
                 tc_wait_ld();
                 float* sc = reinterpret_cast<float*>(sr);
-                if (r == 0) FA_TRACE_EV(w, 6);
 
                 if (fl & (TILE_BOUND | TILE_DOC)) {
                     // keep(x) = (x <= lim) & (qc >= 0 | kc[x] == qc). The compare + select per entry is
@@ -425,7 +412,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     const bool doc = (fl & TILE_DOC) && qc < 0;  // a row with qc >= 0 passes the id check everywhere
                     const int* kcs = reinterpret_cast<const int*>(smem + S::off_kc + ((G + t) % S::NKC) * (kBlk * 4));
                     // (the key codes completed on K's barrier, before the S MMA whose result was just read)
-                    if (r == 0) FA_TRACE_EV(w, 11);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         int state = 0;  // this row in chunk q: 0 keep all, 1 mask all, 2 entry by entry
@@ -462,7 +448,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         }
                     }
                 }
-                if (r == 0) FA_TRACE_EV(w, 7);
                 float mxa[8];
 #pragma unroll
                 for (int a = 0; a < 8; ++a) mxa[a] = max3(sc[a], sc[8 + a], sc[16 + a]);
@@ -498,7 +483,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         tc_wait_st();
                     }
                 }
-                if (r == 0) FA_TRACE_EV(w, 8);
                 m_run = m_new;
                 const float mneg = (m_run == -INFINITY) ? 0.f : -m_run * c;
                 // exp2(s*c - m*c) on packed pairs; P goes to TMEM in two halves so that the first four
@@ -533,7 +517,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(BAR((half ? B_PHALF1 : B_PHALF0) + w));
-                    if (r == 0) FA_TRACE_EV(w, 9 + half);
                 };
                 exp_half(0);
                 exp_half(1);
@@ -549,7 +532,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
             // ------------------------------ item epilogue ------------------------------
             // wait for this group's last P*V, then merge the two partial softmaxes
-            if (r == 0) FA_TRACE_EV(w, 1);
             if (!alive) break;
             if (T == 0) {
                 // nobody has waited for this item's Q load yet, and its slot is about to become the staging
@@ -566,14 +548,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             float* ml = reinterpret_cast<float*>(smem + S::off_ml) + s * (4 * kBlk);  // [2 groups][m, l][128]
             ml[(w * 2 + 0) * kBlk + r] = m_run;
             ml[(w * 2 + 1) * kBlk + r] = l_run;
-            if (r == 0) FA_TRACE_EV(w, 2);
             tc_fence_before();
             mbar_arrive(BAR(B_MLFULL));  // both groups are past all MMAs of this item
             alive = mbar_wait(BAR(B_MLFULL), k & 1, ab, ST_WAIT_TIMEOUT + 16);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
-            if (r == 0) FA_TRACE_EV(w, 3);
             // index 0: the chain of the item's even tiles, 1: of its odd tiles
             const float m0 = ml[(we * 2 + 0) * kBlk + r], l0 = ml[(we * 2 + 1) * kBlk + r];
             const float m1 = ml[((we ^ 1) * 2 + 0) * kBlk + r], l1 = ml[((we ^ 1) * 2 + 1) * kBlk + r];
@@ -635,7 +615,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (healthy) mbar_arrive(BAR(B_OSTAGED + s));  // the producer warp issues the TMA store
             G += T;
             if (r == 0 && alive) mbar_arrive(BAR(B_ITEMEMPTY + s));
-            if (r == 0) FA_TRACE_EV(w, 4);
         }
     }
 
@@ -670,7 +649,6 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
     return cudaGetLastError();
 }
 
-FA_TRACE_DUMP_FN(fa_trace_dump_fwd)
 
 cudaError_t launch_fwd(int D, bool bf16, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                        const CUtensorMap& to, const FwdParams& p, int num_sms, cudaStream_t stream) {
