@@ -29,7 +29,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 import numpy as np
 import torch
 
-import workloads
+from flash_b200 import workloads
 
 METRIC = "effective attention TFLOP/s fwd+bwd (doc-masked bf16)"
 # algorithmic FLOPs per unmasked entry, in units of D: S and P*V forward; S, dP, dV, dK in the

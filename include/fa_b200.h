@@ -10,11 +10,21 @@
  *  - every pointer is a device pointer of the current CUDA device unless stated otherwise;
  *  - tensors are [B, H, L, D] with ELEMENT strides; the last stride must be 1, the other
  *    strides multiples of 8 elements and the base 16-byte aligned (TMA rules);
+ *  - lse, delta and plan buffers must be 16-byte aligned (the kernels read them with bulk copies
+ *    and 16-byte loads); a misaligned buffer is refused with FA_ERR_ALIGNMENT;
  *  - the caller owns every buffer;
  *  - every function enqueues on `stream` and returns without synchronising;
  *  - return value 0 = ok, otherwise an FA_ERR_* code (fa_error_string() describes it);
  *  - `status` is one int32 in device memory, zeroed by the caller. Kernels write a non-zero
- *    code there when a bounded wait ran out (100..199) or an id was out of range (200).
+ *    code there when a bounded wait ran out (100..199) or an id was out of range (200); the
+ *    first code wins. A time-out code is sticky: while the word holds one, every later
+ *    fa_fwd / fa_bwd_dkdv / fa_bwd_dq launch given that word computes nothing and fills its
+ *    outputs (o; dk, dv; dq) with NaN, until the host has read the word and set it back to 0.
+ *    The outputs of the launch in which the wait ran out are undefined. Code 200 only concerns
+ *    the call that passed the id (its result may mask that query wrongly); later calls run.
+ *  - one bounded wait lasts at most 5e8 SM clocks (about 0.25 s); the environment variable
+ *    FA_B200_WAIT_LIMIT_CLOCKS (>= 10000), read when the library is first used, replaces the limit,
+ *    e.g. on hosts where several contexts time-share the GPU.
  */
 #ifndef FA_B200_H_
 #define FA_B200_H_
@@ -133,6 +143,13 @@ int fa_debug_mask(const fa_problem* p, const void* plan, uint8_t* keep, uint8_t*
 int fa_fwd_static_plan(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v,
                        const fa_tensor* o, float* lse, const fa_ids* eq, const fa_ids* ek, int32_t* status,
                        void* stream);
+
+/* Test hook for the failure path (no counterpart in the reference, which has no failure handling):
+ * one warp waits on a barrier nobody arrives at, with the kernels' own bounded wait and a limit of
+ * `limit_clocks` SM clocks. The wait gives up, the kernel returns normally and `*status` holds
+ * 100 + role (role in 0..97). With a few thousand clocks this takes microseconds; nothing faults,
+ * traps or hangs. */
+int fa_debug_wait_timeout(int32_t* status, int64_t limit_clocks, int32_t role, void* stream);
 
 /* Host-only helper, no GPU involved: the tile classification the kernels apply to tile
  * (qb, kb) given the id-code min/max of its query block and key block. Returns the tile_class

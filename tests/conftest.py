@@ -28,3 +28,25 @@ def _built_library():
         import build
         build.build()
     return so
+
+
+# largest errors seen by the GPU parity tests: (test, output) -> (max-abs, max-abs over elements below 2.56)
+_ERRORS = {}
+
+
+def record_error(test, what, worst, worst_small):
+    key = (test, what)
+    old = _ERRORS.get(key, (0.0, 0.0))
+    _ERRORS[key] = (max(old[0], worst), max(old[1], worst_small))
+
+
+def pytest_terminal_summary(terminalreporter):
+    if not _ERRORS:
+        return
+    tr = terminalreporter
+    tr.write_line("largest absolute errors against the fp32 reference evaluation (all / elements with |ref| < 2.56):")
+    per_test = {}
+    for (test, what), (a, b) in _ERRORS.items():
+        per_test.setdefault(test, []).append(f"{what.split()[-1] if ' ' in what else what} {a:.4f}/{b:.4f}")
+    for test, items in per_test.items():
+        tr.write_line(f"  {test}: " + "  ".join(items[:12]) + (" ..." if len(items) > 12 else ""))

@@ -19,7 +19,7 @@ import sys
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(HERE, ".."))
+sys.path.insert(0, os.path.join(HERE, "..", "..", "triton-flash-attention-with-flexible-masks_b200"))
 REF = os.environ.get("FA_REFERENCE")
 if not REF or not os.path.isdir(REF):
     sys.exit("set FA_REFERENCE to the directory of the reference checkout")
@@ -32,7 +32,7 @@ torch.cuda.get_device_capability = lambda *a, **k: (10, 0)  # testing.py:22 / fl
 import testing as ref_testing  # noqa: E402
 import flash_triton as ref_flash  # noqa: E402
 
-import workloads  # noqa: E402
+from flash_b200 import workloads  # noqa: E402
 
 
 def small_cases():

@@ -18,7 +18,7 @@ def _declared(repo_root):
 def test_every_declared_symbol_is_exported(repo_root):
     lib = ctypes.CDLL(_lib.LIB_PATH)
     names = _declared(repo_root)
-    assert len(names) >= 11
+    assert len(names) >= 13
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/fa_b200.h but not exported"
     assert set(_lib.EXPORTS) <= set(names)
@@ -34,7 +34,7 @@ def test_version_and_strings():
     lib = _lib.load()
     assert lib.fa_version() == 1
     assert lib.fa_error_string(0) == b"ok"
-    assert b"TMA" in lib.fa_error_string(3)
+    assert b"aligned" in lib.fa_error_string(3)
     assert lib.fa_padded_rows(1) == 128 and lib.fa_padded_rows(128) == 128 and lib.fa_padded_rows(129) == 256
 
 
@@ -93,3 +93,37 @@ def test_forward_refuses_bad_tensors_without_a_gpu():
     rc = lib.fa_fwd(ctypes.byref(_prob()), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t),
                     ctypes.cast(lse, ctypes.c_void_p), None, ctypes.cast(ctypes.pointer(st), ctypes.c_void_p), None)
     assert rc == 6
+
+
+def test_per_row_buffers_and_plan_must_be_16_byte_aligned():
+    """lse, delta and the plan are read with bulk copies and 16-byte loads: a buffer that is only 4-byte aligned
+    is refused with FA_ERR_ALIGNMENT before anything is launched."""
+    lib = _lib.load()
+    t = _lib.Tensor()
+    t.ptr = 0x1000
+    for i, s in enumerate((1 << 20, 1 << 16, 128, 1)):
+        t.stride[i] = s
+    T = ctypes.byref(t)
+    st = ctypes.cast(ctypes.pointer(ctypes.c_int32(0)), ctypes.c_void_p)
+    good, bad = ctypes.c_void_p(0x2000), ctypes.c_void_p(0x2004)
+    p0, p1 = ctypes.byref(_prob(mode=0)), ctypes.byref(_prob())
+    assert lib.fa_fwd(p0, T, T, T, T, bad, None, st, None) == 3
+    assert lib.fa_fwd(p0, T, T, T, T, good, bad, st, None) == 3          # the plan (work counters)
+    assert lib.fa_fwd(p1, T, T, T, T, good, bad, st, None) == 3
+    assert lib.fa_bwd_delta(p0, T, T, bad, None) == 3
+    assert lib.fa_bwd_dkdv(p0, T, T, T, T, bad, good, T, T, None, st, None) == 3
+    assert lib.fa_bwd_dkdv(p0, T, T, T, T, good, bad, T, T, None, st, None) == 3
+    assert lib.fa_bwd_dkdv(p0, T, T, T, T, good, good, T, T, bad, st, None) == 3
+    assert lib.fa_bwd_dq(p0, T, T, T, T, bad, good, T, None, st, None) == 3
+    assert lib.fa_bwd_dq(p0, T, T, T, T, good, bad, T, None, st, None) == 3
+    assert lib.fa_bwd_dq(p0, T, T, T, T, good, good, T, bad, st, None) == 3
+    assert lib.fa_debug_mask(p1, bad, None, None, None) == 3
+    assert b"lse" in lib.fa_error_string(3)
+
+
+def test_wait_test_hook_checks_its_arguments():
+    lib = _lib.load()
+    st = ctypes.cast(ctypes.pointer(ctypes.c_int32(0)), ctypes.c_void_p)
+    assert lib.fa_debug_wait_timeout(None, 1000, 1, None) == 1
+    assert lib.fa_debug_wait_timeout(st, 0, 1, None) == 1
+    assert lib.fa_debug_wait_timeout(st, 1000, 98, None) == 1

@@ -2,10 +2,12 @@
 against the CPU oracle on the same seeded inputs, against the golden fixtures generated from
 the reference, and through size-independent properties at the full benchmark sizes.
 
-Tolerances (from the task statement): the keep/mask pattern is bit-exact; O, dQ, dK, dV are
-within max-abs 2e-2 of an fp32 evaluation for bf16/fp16. A result of magnitude above 2.56 cannot
-be represented in bf16 more closely than 2^-8 of its value, so the bound used per element is
-max(2e-2, 2^-7 * |reference|); the plain 2e-2 is asserted wherever the data allows it.
+Tolerances: the keep/mask pattern is bit-exact; O, dQ, dK, dV are within max-abs 2e-2 of an fp32
+evaluation. That plain bound is asserted for every fp16 result and for every bf16 element whose
+reference magnitude is below 2.56. A bf16 number of magnitude 2.56 or more has a spacing of 2^-6 or
+more, so its rounding alone can cost 2^-7 of the value: only for those elements the bound is
+2^-7 * |reference|. The largest error of every output of every case is collected and printed in the
+terminal summary of the run.
 """
 import glob
 import math
@@ -16,7 +18,7 @@ import pytest
 import torch
 
 import attention_oracle as orc
-import workloads
+from flash_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
@@ -32,14 +34,24 @@ def fb():
 
 
 def close(got, ref, what, strict=False):
+    """`strict`: the plain 2e-2 for every element, whatever the dtype."""
+    bf16 = got.dtype == torch.bfloat16
     got = got.detach().float().cpu()
     ref = ref.detach().float().cpu()
     assert torch.isfinite(got).all(), f"{what}: non-finite values"
     err = (got - ref).abs()
-    bound = torch.full_like(ref, TOL) if strict else torch.maximum(torch.full_like(ref, TOL), ref.abs() * 2.0 ** -7)
+    bound = torch.full_like(ref, TOL)
+    if bf16 and not strict:
+        bound = torch.where(ref.abs() < 2.56, bound, ref.abs() * 2.0 ** -7)
     bad = err > bound
-    assert not bad.any(), f"{what}: max-abs error {err.max().item():.4f}, {int(bad.sum())} entries over the bound"
-    return err.max().item()
+    worst = err.max().item()
+    small = ref.abs() < 2.56
+    worst_small = err[small].max().item() if small.any() else 0.0
+    import conftest
+    conftest.record_error(os.environ.get("PYTEST_CURRENT_TEST", "?").split("::")[-1].split(" ")[0], what, worst, worst_small)
+    assert not bad.any(), (f"{what}: max-abs error {worst:.4f} (elements below 2.56: {worst_small:.4f}), "
+                           f"{int(bad.sum())} entries over the bound")
+    return worst
 
 
 def make_ids(B, H, L, ndoc, pos_frac, rng, per_head=False):
@@ -169,10 +181,9 @@ def test_parity_int32_ids(fb):
                                         if not p.endswith("c0.npz")))
 def test_golden_fixtures_from_the_reference(fb, name):
     """fp16 run on the fixture's inputs against the reference's own outputs (`_attn_torch` and
-    the Triton operator under the interpreter). The fixtures use D=64 (D=32 is not implemented)."""
+    the Triton operator under the interpreter). Head dims below 64 (the grouped-query fixture has D=32)
+    go through the operator's zero-padded path."""
     z = np.load(os.path.join(GOLD, name + ".npz"))
-    if z["q"].shape[-1] not in (64, 128):
-        pytest.skip("head dim of this fixture is outside the implemented set {64, 128}")
     causal, mode = bool(z["causal"]), int(z["mode"])
     q, k, v, do = [torch.from_numpy(z[x]).to("cuda", FP) for x in ("q", "k", "v", "do")]
     q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
@@ -207,8 +218,8 @@ def test_config0_against_the_reference_fixture(fb):
     fb.check_status()
 
 
-def _check_heads(fb, name, heads, B=None, backward=True, strict_o=True):
-    w = workloads.make_inputs(name, device="cuda", B=B)
+def _check_heads(fb, name, heads, B=None, backward=True, strict_o=True, always_attend=0.0):
+    w = workloads.make_inputs(name, device="cuda", B=B, always_attend=always_attend)
     cfg = w["cfg"]
     q, k, v = [w[x].requires_grad_() for x in "qkv"]
     o = fb.attention(q, k, v, w["causal"], w["sm_scale"], w["eq"], w["ek"], w["mode"])
@@ -239,12 +250,18 @@ def test_config2_full_size(fb):
     _check_heads(fb, "c2", [(0, 0), (7, 7)])
 
 
-def test_config3_full_size_one_head(fb):
-    _check_heads(fb, "c3", [(0, 5)])
+def test_config1_full_size_with_always_attend_positions(fb):
+    """Configuration 1 read literally ("ids as in config 0"): 5 % of the positions carry an id >= 0, so
+    nearly every tile needs the id check and none of a document's later tiles can be skipped."""
+    _check_heads(fb, "c1", [(1, 3), (2, 9)], always_attend=0.05)
 
 
-def test_config4_forward_two_batches(fb):
-    _check_heads(fb, "c4", [(1, 31)], B=2, backward=False)
+def test_config3_full_size_four_heads(fb):
+    _check_heads(fb, "c3", [(0, 0), (0, 5), (0, 17), (0, 31)])
+
+
+def test_config4_forward_and_backward_two_batches(fb):
+    _check_heads(fb, "c4", [(1, 31), (0, 7)], B=2, backward=True)
 
 
 @pytest.mark.parametrize("name", ["c0", "c1", "c2"])
@@ -406,9 +423,12 @@ def test_unsupported_inputs_raise(fb):
 
 
 def test_id_out_of_int32_range_is_reported(fb):
-    z = torch.zeros(1, 1, 128, 64, dtype=BF, device="cuda")
+    z = torch.ones(1, 1, 128, 64, dtype=BF, device="cuda")
     ids = torch.full((1, 1, 128), -(2 ** 40), dtype=torch.int64, device="cuda")
     fb.attention(z, z, z, False, None, ids, ids, 1)
+    # the error concerns that call only: a later, unrelated call still computes although the word is set
+    o = fb.attention(z, z, z)
+    assert (o.float() - 1).abs().max().item() < 1e-2
     with pytest.raises(RuntimeError, match="int32"):
         fb.check_status()
     fb.check_status()  # the status word is cleared by the failed check
@@ -416,7 +436,8 @@ def test_id_out_of_int32_range_is_reported(fb):
 
 def test_status_word_plumbing(fb):
     """Failure detection without a GPU fault: the host reads the status word a kernel would set
-    when one of its bounded waits runs out."""
+    when one of its bounded waits runs out; while the word is set, the kernels compute nothing and
+    fill their outputs with NaN, so that no later result can be mistaken for a valid one."""
     from flash_b200 import ops
     z = torch.zeros(1, 1, 128, 64, dtype=BF, device="cuda")
     fb.attention(z, z, z)
@@ -424,11 +445,84 @@ def test_status_word_plumbing(fb):
     ops._status_word(z.device).fill_(107)
     with pytest.raises(RuntimeError, match="bounded wait"):
         fb.check_status()
-    # a set status word makes the kernels return at once instead of computing
     ops._status_word(z.device).fill_(107)
-    o = fb.attention(torch.ones_like(z), torch.ones_like(z), torch.ones_like(z))
+    one = torch.ones(2, 4, 300, 128, dtype=BF, device="cuda")
+    q, k, v = [one.clone().requires_grad_() for _ in range(3)]
+    o = fb.attention(q, k[:, :2], v[:, :2], True)
+    o.backward(one)
+    assert torch.isnan(o).all() and torch.isnan(q.grad).all() and torch.isnan(k.grad[:, :2]).all() and torch.isnan(v.grad[:, :2]).all()
     with pytest.raises(RuntimeError):
         fb.check_status()
-    o = fb.attention(torch.ones_like(z), torch.ones_like(z), torch.ones_like(z))
+    o = fb.attention(one, one, one)
     fb.check_status()
     assert (o.float() - 1).abs().max().item() < 1e-2
+
+
+def test_bounded_wait_gives_up_and_reports(fb):
+    """The kernels' own bounded wait, run in the open by a one-warp test kernel: it waits on a barrier
+    nobody arrives at, gives up after a few thousand clocks, returns normally and leaves 100 + role in
+    the status word. Nothing faults, traps or hangs; the context stays usable."""
+    import ctypes
+    from flash_b200 import _lib, ops
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fb.check_status()
+    st = ops._status_word(dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    assert lib.fa_debug_wait_timeout(st.data_ptr(), 20000, 42, stream) == 0
+    t1.record()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 142
+    assert t0.elapsed_time(t1) < 50.0  # ms; the wait itself lasts about 10 microseconds
+    with pytest.raises(RuntimeError, match="role 42"):
+        fb.check_status()
+    z = torch.ones(1, 1, 128, 64, dtype=BF, device="cuda")
+    assert (fb.attention(z, z, z).float() - 1).abs().max().item() < 1e-2  # the device is still usable
+    fb.check_status()
+
+
+def test_tensors_on_another_device_are_refused(fb):
+    q = torch.zeros(1, 1, 128, 64, dtype=BF, device="cuda")
+    with pytest.raises(ValueError, match="same CUDA device"):
+        fb.attention(q, q.cpu(), q)
+    ids = torch.zeros(1, 1, 128, dtype=torch.int64)
+    with pytest.raises(ValueError, match="same CUDA device"):
+        fb.attention(q, q, q, False, None, ids, ids, 1)
+    with pytest.raises(ValueError, match="one dtype"):
+        fb.attention(q, q.half(), q)
+
+
+def test_skipping_and_chunk_shortcuts_do_not_change_results(fb, monkeypatch):
+    """FA_B200_ALL_PARTIAL evaluates the mask entry by entry on every visited tile: bit-identical results.
+    FA_B200_NO_SKIP also visits the tiles the ids mask entirely: the backward, whose accumulation order does
+    not change, stays bit-identical for the same forward results; the forward deals its tiles to two
+    accumulation chains by their position in the walk, so its last bits may move."""
+    w = workloads.make_inputs("c1", device="cuda", B=2, H=4, always_attend=0.01)
+    args = (w["causal"], w["sm_scale"], w["eq"], w["ek"], w["mode"])
+
+    def run():
+        q, k, v = [w[x].detach().clone().requires_grad_() for x in "qkv"]
+        o = fb.attention(q, k, v, *args)
+        o.backward(w["do"])
+        torch.cuda.synchronize()
+        return o.detach(), q.grad, k.grad, v.grad
+
+    base = run()
+    _, cls0 = fb.debug_mask(2, 4, w["cfg"]["M"], w["cfg"]["N"], *args[:1], w["eq"], w["ek"], 1)
+    monkeypatch.setenv("FA_B200_ALL_PARTIAL", "1")
+    for a, b in zip(base, run()):
+        assert torch.equal(a, b)
+    _, cls1 = fb.debug_mask(2, 4, w["cfg"]["M"], w["cfg"]["N"], *args[:1], w["eq"], w["ek"], 1)
+    assert torch.equal(cls0 & 1, cls1 & 1) and bool(((cls1 & 1) == ((cls1 >> 2) & 1)).all())
+    monkeypatch.delenv("FA_B200_ALL_PARTIAL")
+    monkeypatch.setenv("FA_B200_NO_SKIP", "1")
+    noskip = run()
+    _, cls2 = fb.debug_mask(2, 4, w["cfg"]["M"], w["cfg"]["N"], *args[:1], w["eq"], w["ek"], 1)
+    nb = w["cfg"]["M"] // 128
+    assert int((cls2 & 1).sum()) == 2 * nb * (nb + 1) // 2 > int((cls0 & 1).sum())  # the whole causal triangle
+    for a, b, name in zip(base, noskip, ("O", "dQ", "dK", "dV")):
+        assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -6 * max(1.0, b.float().abs().max().item()), name
+    monkeypatch.delenv("FA_B200_NO_SKIP")
+    fb.check_status()

@@ -52,6 +52,25 @@ def test_no_cpu_fallback():
         fb.attention(q, q, q)
 
 
+def test_tensors_of_one_call_must_share_a_device():
+    """Every pointer is dereferenced on q's device: a k, v, eq, ek or dO that lives elsewhere is refused by the
+    wrapper before anything is launched (checked here without a GPU, on the helper the operator calls)."""
+    from flash_b200 import ops
+    q = torch.zeros(1, 1, 8, 8)
+    other = torch.zeros(1, 1, 8, 8, device="meta")
+    ops._same_device(q, k=q, v=q, eq=None, ek=None)
+    with pytest.raises(ValueError, match="same CUDA device"):
+        ops._same_device(q, k=q, v=other)
+    with pytest.raises(ValueError, match="ek is on meta"):
+        ops._same_device(q, eq=None, ek=other)
+    # the mask materialiser refuses ids that are not on its device (no launch: the check comes first)
+    ids = torch.zeros(1, 1, 64, dtype=torch.int64)
+    with pytest.raises(ValueError, match="eq is on cpu"):
+        fb.debug_mask(1, 1, 64, 64, True, ids, ids, 1, device="cuda:0")
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        fb.debug_mask(1, 1, 64, 64, True, ids, ids, 1, device="cpu")
+
+
 def test_maybe_contiguous_rules():
     x = torch.zeros(2, 2, 16, 64, dtype=torch.bfloat16)
     assert fb.maybe_contiguous(x) is x

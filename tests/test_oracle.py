@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import attention_oracle as orc
-import workloads
+from flash_b200 import workloads
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 SMALL = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")) if not p.endswith("c0.npz"))

@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", "oracle"))
-import attention_oracle as orc  # noqa: E402
+import attention_oracle as orc
+import conftest  # noqa: E402
 
 
 def _ids(B, He, L, kind, nrng):
@@ -92,5 +93,10 @@ def test_random_sweep(seed):
             got = got.detach().float().cpu()
             assert torch.isfinite(got).all(), (what, name)
             err = (got - r).abs()
-            bound = torch.full_like(r, 2e-2) if name == "O" else torch.clamp(r.abs() * 2 ** -6, min=3e-2)
-            assert bool((err <= bound).all()), (what, name, float(err.max()))
+            # the rule of test_attention_gpu.close: 2e-2, except where a bf16 number cannot be that close
+            bound = torch.full_like(r, 2e-2)
+            if dt == torch.bfloat16 and name != "O":
+                bound = torch.where(r.abs() < 2.56, bound, r.abs() * 2.0 ** -7)
+            small = r.abs() < 2.56
+            conftest.record_error(f"sweep seed {seed}", name, float(err.max()), float(err[small].max()) if small.any() else 0.0)
+            assert bool((err <= bound).all()), (what, name, float(err.max()), float((err - bound).max()))

@@ -9,7 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import attention_oracle as orc
-import workloads
+from flash_b200 import workloads
 from flash_b200 import shard
 
 

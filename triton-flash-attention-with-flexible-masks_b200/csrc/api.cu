@@ -1,5 +1,6 @@
 // extern "C" surface of the library (declared in include/fa_b200.h): argument checks, TMA
 // tensor-map encoding, parameter packing and launches. Nothing here allocates or synchronises.
+#include <cstdlib>
 #include <mutex>
 #include "../../include/fa_b200.h"
 #include "common.cuh"
@@ -89,8 +90,23 @@ int make_map(CUtensorMap* out, const fa_tensor* t, int dtype, int B, int H, int 
 
 constexpr size_t kCtrWords = 128;  // size of the plan's counter section (PlanLayout::off_ctr)
 
+// Debug switches, read from the environment at every call so that a test can flip them:
+// FA_B200_NO_SKIP=1 visits every tile inside the causal / length bound, FA_B200_ALL_PARTIAL=1 evaluates
+// the mask entry by entry on every visited tile. Results do not change (the forward's last bits can, with
+// FA_B200_NO_SKIP, because tiles are dealt to its two accumulation chains by their position in the walk).
+int debug_flags() {
+    auto on = [](const char* name) {
+        const char* e = getenv(name);
+        return e && e[0] != '\0' && !(e[0] == '0' && e[1] == '\0');
+    };
+    return (on("FA_B200_NO_SKIP") ? fa::DBG_NO_SKIP : 0) | (on("FA_B200_ALL_PARTIAL") ? fa::DBG_ALL_PARTIAL : 0);
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
 int make_mask(fa::MaskArgs* m, const fa_problem* p, const void* plan) {
     if (p->mode == FA_MODE1_DOC && !plan) return FA_ERR_PLAN_SIZE;
+    if (!aligned16(plan)) return FA_ERR_ALIGNMENT;  // the kernels read it with 16-byte and bulk loads
     m->plan = (p->mode == FA_MODE1_DOC) ? static_cast<const int32_t*>(plan) : nullptr;
     m->He = (p->mode == FA_MODE1_DOC) ? p->id_heads : 1;
     m->L = fa::PlanLayout(p->B, m->He, p->M, p->N);
@@ -102,12 +118,27 @@ int make_mask(fa::MaskArgs* m, const fa_problem* p, const void* plan) {
     m->gap = p->N > p->M ? p->N - p->M : 0;  // flash_triton.py:521
     m->causal = p->causal ? 1 : 0;
     m->mode = p->mode;
+    m->debug = debug_flags();
     return FA_OK;
 }
 
 fa::OutTensor out_view(const fa_tensor* t) { return fa::OutTensor{t->ptr, t->stride[0], t->stride[1], t->stride[2]}; }
 
 constexpr float kLog2e = 1.4426950408889634f;
+
+// Limit of one bounded wait inside the kernels, in SM clocks: FA_B200_WAIT_LIMIT_CLOCKS if set to a
+// number >= 10000 when the library is first used, else the built-in default.
+long long wait_limit_clocks() {
+    static const long long v = [] {
+        const char* e = getenv("FA_B200_WAIT_LIMIT_CLOCKS");
+        if (e) {
+            const long long x = atoll(e);
+            if (x >= 10000) return x;
+        }
+        return fa::kWaitLimitClocks;
+    }();
+    return v;
+}
 
 // Number of SMs of the current device (persistent kernels launch one CTA per SM); cached per device.
 // Heads per scheduling group of the persistent kernels (see their `decode`): as many heads as
@@ -155,7 +186,8 @@ const char* fa_error_string(int code) {
             return "unsupported problem (head dim must be 64 or 128, dtype bf16/fp16, sm_scale > 0, "
                    "at most 131072 tokens per sequence)";
         case FA_ERR_ALIGNMENT:
-            return "tensor breaks the TMA rules (16-byte aligned base, last stride 1, other strides multiples of 8)";
+            return "a buffer breaks the alignment rules (tensors: 16-byte aligned base, last stride 1, other strides "
+                   "multiples of 8; lse, delta and plan: 16-byte aligned)";
         case FA_ERR_TENSORMAP: return "cuTensorMapEncodeTiled failed";
         case FA_ERR_LAUNCH: return "kernel launch failed";
         case FA_ERR_PLAN_SIZE: return "mask plan missing or too small";
@@ -209,6 +241,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     int rc = check_problem(p);
     if (rc) return rc;
     if (!lse || !status) return FA_ERR_BAD_ARG;
+    if (!aligned16(lse)) return FA_ERR_ALIGNMENT;
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
     if ((rc = check_tensor(v, p->B, p->Hk, p->N))) return rc;
@@ -230,6 +263,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     fp.by_length = (p->mode == FA_MODE1_DOC && int64_t(fa::cdiv(p->M, fa::kBlk) * p->H * p->B) < 32 * int64_t(sms)) ? 1 : 0;
     fp.scale_log2 = p->sm_scale * kLog2e;
     fp.status = status;
+    fp.wait_limit = wait_limit_clocks();
     const cudaError_t e =
         fa::launch_fwd(p->D, p->dtype == FA_BF16, tq, tk, tv, to, fp, sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
@@ -239,6 +273,7 @@ int fa_bwd_delta(const fa_problem* p, const fa_tensor* o, const fa_tensor* d_o, 
     int rc = check_problem(p);
     if (rc) return rc;
     if (!delta) return FA_ERR_BAD_ARG;
+    if (!aligned16(delta)) return FA_ERR_ALIGNMENT;
     if ((rc = check_tensor(o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     fa::DeltaParams dp;
@@ -258,6 +293,7 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     int rc = check_problem(p);
     if (rc) return rc;
     if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
+    if (!aligned16(lse) || !aligned16(delta)) return FA_ERR_ALIGNMENT;  // read with bulk copies
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
@@ -287,6 +323,7 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     kp.scale_log2 = p->sm_scale * kLog2e;
     kp.sm_scale = p->sm_scale;
     kp.status = status;
+    kp.wait_limit = wait_limit_clocks();
     const cudaError_t e =
         fa::launch_bwd_dkdv(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdk, tdv, kp, sms,
                             static_cast<cudaStream_t>(stream));
@@ -299,6 +336,7 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     int rc = check_problem(p);
     if (rc) return rc;
     if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
+    if (!aligned16(lse) || !aligned16(delta)) return FA_ERR_ALIGNMENT;  // read with bulk copies
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(dq, p->B, p->H, p->M))) return rc;
@@ -325,6 +363,7 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     qp.scale_log2 = p->sm_scale * kLog2e;
     qp.sm_scale = p->sm_scale;
     qp.status = status;
+    qp.wait_limit = wait_limit_clocks();
     const cudaError_t e =
         fa::launch_bwd_dq(p->D, p->dtype == FA_BF16, tq, tk, tv, tdo, tdq, qp, sms, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;

@@ -135,7 +135,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               B_PFULL = B_SFULL + 3, B_PFREE = B_SFULL + 4, B_DSFULL = B_SFULL + 5, B_DONE = B_SFULL + 6,
               B_ACCFREE = B_SFULL + 7, B_STAGED = B_SFULL + 8, B_STAGEFREE = B_SFULL + 9, B_ITEMFULL = B_SFULL + 10,
               B_ITEMEMPTY = B_ITEMFULL + 2, B_VEMPTY = B_ITEMEMPTY + 2;
-    Abort ab{misc + 1, p.status};
+    Abort ab{misc + 1, p.status, p.wait_limit};
 
     const uint32_t sK = sbase + S::off_k, sV = sbase + S::off_v, sP = sbase + S::off_p;
     auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
@@ -165,7 +165,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_init(BAR(B_ITEMFULL + s), 1);
             mbar_init(BAR(B_ITEMEMPTY + s), 11);  // producer, two MMA issuers, eight compute warps
         }
-        misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
+        misc[1] = (status_is_fatal(*reinterpret_cast<volatile int*>(p.status)) || (sbase & 1023u) != 0) ? 1 : 0;
         fence_mbar_init();
     }
     if (warp == 9) {
@@ -177,6 +177,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = uint32_t(misc[0]);
     const bool aborted = misc[1] != 0;
+    // an earlier launch on this device ran into a time-out that the host has not yet cleared
+    if (aborted && (sbase & 1023u) == 0) nan_fill_outputs(smem + S::off_k, S::NBOX, &tmdK, &tmdV, nK, p.Hk, p.B);
 
     if (warp >= 8) {
         setmaxnreg_dec<56>();

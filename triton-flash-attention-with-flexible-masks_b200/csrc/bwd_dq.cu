@@ -97,7 +97,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     constexpr int B_ITEMFULL = 0, B_ITEMEMPTY = 2, B_QFULL = 4, B_STAGED = 6, B_DOFULL = 8, B_DOEMPTY = 9, B_VFULL = 10,
                   B_VEMPTY = 11, B_KFULL = 12, B_KEMPTY = 12 + NSK, B_SFULL = 12 + 2 * NSK, B_DSFULL = B_SFULL + 2,
                   B_DPFULL = B_SFULL + 4, B_DONE = B_SFULL + 5, B_ACCFREE = B_SFULL + 6;
-    Abort ab{misc + 1, p.status};
+    Abort ab{misc + 1, p.status, p.wait_limit};
 
     auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
     const uint32_t sdO = sbase + S::off_do, sV = sbase + S::off_v;
@@ -120,7 +120,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         mbar_init(BAR(B_DPFULL), 1);
         mbar_init(BAR(B_DONE), 1);
         mbar_init(BAR(B_ACCFREE), 256);
-        misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
+        misc[1] = (status_is_fatal(*reinterpret_cast<volatile int*>(p.status)) || (sbase & 1023u) != 0) ? 1 : 0;
         fence_mbar_init();
     }
     if (warp == 9) {
@@ -132,6 +132,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     tc_fence_after();
     const uint32_t tmem = uint32_t(misc[0]);
     const bool aborted = misc[1] != 0;
+    // an earlier launch on this device ran into a time-out that the host has not yet cleared
+    if (aborted && (sbase & 1023u) == 0) nan_fill_outputs(smem + S::off_q, S::NBOX, &tmdQ, nullptr, nQ, p.H, p.B);
 
     if (warp >= 8) {
         setmaxnreg_dec<56>();

@@ -73,6 +73,14 @@ struct MaskArgs {
     PlanLayout L;
     int M, N, gap, causal, mode;
     int He;               // 1 or H
+    int debug;            // DBG_* bits (0 in normal use)
+};
+
+// Debug switches that change which tiles are visited and how they are evaluated, never the result:
+// they exist to show that skipping tiles and the per-chunk shortcuts are exact.
+enum : int {
+    DBG_NO_SKIP = 1,      // visit every tile inside the causal / length bound, also those the ids mask entirely
+    DBG_ALL_PARTIAL = 2,  // evaluate the bound and the id rule entry by entry on every visited tile
 };
 
 enum { CTR_FWD = 0, CTR_DKDV = 2, CTR_DQ = 4 };  // pairs {next item, CTAs finished} inside the plan's ctr section
@@ -119,6 +127,13 @@ __device__ __forceinline__ uint32_t classify_from_plan(const MaskArgs& a, int b,
         kmax = a.plan[a.L.off_kmax + bh * a.L.nK + kb];
     }
     uint32_t f = classify_tile(qb, kb, a.M, a.N, a.gap, a.causal, a.mode, qmin, qmax, kmin, kmax);
+    if (a.debug) {
+        if ((a.debug & DBG_NO_SKIP) && f == 0 && a.mode == 1) {
+            f = classify_tile(qb, kb, a.M, a.N, a.gap, a.causal, 0, 0, 0, 0, 0);  // the bounds alone
+            if (f) f |= TILE_DOC;                                                // the ids mask every entry
+        }
+        if ((a.debug & DBG_ALL_PARTIAL) && f) return f | TILE_BOUND | (a.mode == 1 ? TILE_DOC : 0u);
+    }
     if (a.mode == 1 && (f & TILE_DOC)) {
         const int64_t bh = int64_t(b) * a.He + he;
         if (a.plan[a.L.off_kmono + bh * a.L.nK + kb]) f |= TILE_KMONO;
@@ -129,7 +144,7 @@ __device__ __forceinline__ uint32_t classify_from_plan(const MaskArgs& a, int b,
 
 // Key-block range [lo, hi) a query block has to walk.
 __device__ __forceinline__ void kv_range(const MaskArgs& a, int b, int he, int qb, int& lo, int& hi) {
-    if (a.mode == 1) {
+    if (a.mode == 1 && !(a.debug & DBG_NO_SKIP)) {
         const int64_t bh = int64_t(b) * a.He + he;
         lo = a.plan[a.L.off_kvlo + bh * a.L.nQ + qb];
         hi = a.plan[a.L.off_kvhi + bh * a.L.nQ + qb];
@@ -144,7 +159,7 @@ __device__ __forceinline__ void kv_range(const MaskArgs& a, int b, int he, int q
 }
 // Query-block range [lo, hi) a key block has to walk.
 __device__ __forceinline__ void q_range(const MaskArgs& a, int b, int he, int kb, int& lo, int& hi) {
-    if (a.mode == 1) {
+    if (a.mode == 1 && !(a.debug & DBG_NO_SKIP)) {
         const int64_t bh = int64_t(b) * a.He + he;
         lo = a.plan[a.L.off_qlo + bh * a.L.nK + kb];
         hi = a.plan[a.L.off_qhi + bh * a.L.nK + kb];
@@ -167,6 +182,32 @@ __device__ __forceinline__ bool keep_entry(int i, int j, int qc, int kc, int N, 
     if (causal) keep = keep && (gap + i >= j);
     if (mode == 1) keep = keep && ((qc >= 0) || (qc == kc));
     return keep;
+}
+
+// A launch that finds the device's status word set by an earlier time-out computes nothing. It fills
+// its outputs with NaN (0xFFFF is a NaN in bf16 and in fp16), so that what it leaves behind cannot be
+// mistaken for a result. Called by all threads of the CTA; `tile` is nbox * 16 KB of shared memory,
+// 1024-byte aligned; m1 may be null. Tiles are [128 rows, 64 * nbox columns] of a [B, H, L, D] tensor.
+__device__ __forceinline__ void nan_fill_outputs(uint8_t* tile, int nbox, const CUtensorMap* m0, const CUtensorMap* m1,
+                                                 int n_blk, int n_h, int n_b) {
+    constexpr int kBox = kBlk * 64 * 2;
+    for (int i = threadIdx.x; i < nbox * kBox / 16; i += blockDim.x)
+        reinterpret_cast<uint4*>(tile)[i] = make_uint4(~0u, ~0u, ~0u, ~0u);
+    fence_proxy_async();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t src = smem_u32(tile);
+        const int n = n_blk * n_h * n_b;
+        for (int j = blockIdx.x; j < n; j += gridDim.x) {
+            const int blk = j % n_blk, h = (j / n_blk) % n_h, b = j / (n_blk * n_h);
+            for (int x = 0; x < nbox; ++x) {
+                tma_store_4d(m0, src + x * kBox, x * 64, blk * kBlk, h, b);
+                if (m1) tma_store_4d(m1, src + x * kBox, x * 64, blk * kBlk, h, b);
+            }
+            tma_store_commit();
+        }
+        tma_store_wait_all();
+    }
 }
 
 // Device-side view of a [B, H, L, D] tensor for plain (non-TMA) stores.

@@ -78,7 +78,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     constexpr int B_ITEMFULL = 0, B_ITEMEMPTY = 2, B_QFULL = 4, B_OSTAGED = 6, B_KFULL = 8, B_KEMPTY = 8 + NS,
                   B_VFULL = 8 + 2 * NS, B_VEMPTY = 8 + 3 * NS, B_SFULL = 8 + 4 * NS, B_PHALF0 = B_SFULL + 2,
                   B_PHALF1 = B_SFULL + 4, B_PVDONE = B_SFULL + 6, B_TURN = B_SFULL + 8, B_OFREE = B_SFULL + 10, B_MLFULL = B_SFULL + 12;
-    Abort ab{misc + 1, p.status};
+    Abort ab{misc + 1, p.status, p.wait_limit};
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) {
@@ -100,7 +100,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             mbar_init(BAR(B_VFULL + s), 1);
             mbar_init(BAR(B_VEMPTY + s), 1);
         }
-        misc[1] = (*reinterpret_cast<volatile int*>(p.status) != 0 || (sbase & 1023u) != 0) ? 1 : 0;
+        misc[1] = (status_is_fatal(*reinterpret_cast<volatile int*>(p.status)) || (sbase & 1023u) != 0) ? 1 : 0;
         fence_mbar_init();
     }
     if (warp == 9) {
@@ -112,6 +112,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     tc_fence_after();
     const uint32_t tmem = uint32_t(misc[0]);
     const bool aborted = misc[1] != 0;
+    // an earlier launch on this device ran into a time-out that the host has not yet cleared
+    if (aborted && (sbase & 1023u) == 0) nan_fill_outputs(smem + S::off_q, S::NBOX, &tmO, nullptr, nQ, p.H, p.B);
 
     auto sQ = [&](int s) { return sbase + S::off_q + uint32_t(s) * S::TILE; };
     auto sK = [&](int s) { return sbase + S::off_k + uint32_t(s) * S::TILE; };

@@ -12,7 +12,8 @@
 // Rules that follow from sharing one array:
 //  - problems whose plan is larger than FA_STATIC_PLAN_BYTES are refused with FA_ERR_SCRATCH_LIMIT;
 //  - the array keeps whatever the previous call left in it. Nothing in it has to start at zero:
-//    the two plan kernels overwrite every element the forward kernel reads, so no clearing is done;
+//    the plan kernels (or, without ids, one 512-byte memset of the work counters) overwrite every
+//    element the forward kernel reads, so no other clearing is done;
 //  - two calls that are in flight on the same GPU at the same time (different streams) write and
 //    read the same array and race. Serialise them on one stream or with events;
 //  - the plan is not returned, so the backward entry points (which want the plan again) need a

@@ -15,6 +15,7 @@ struct FwdParams {
     int by_length;     // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2;  // sm_scale * log2(e)
     int* status;
+    long long wait_limit;  // SM clocks a bounded wait may last
 };
 
 struct DeltaParams {
@@ -34,6 +35,7 @@ struct DkdvParams {
     int by_length;  // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2, sm_scale;
     int* status;
+    long long wait_limit;  // SM clocks a bounded wait may last
 };
 
 struct DqParams {
@@ -45,6 +47,7 @@ struct DqParams {
     int by_length;  // take the blocks of a head in the plan's sorted order (few items per CTA)
     float scale_log2, sm_scale;
     int* status;
+    long long wait_limit;  // SM clocks a bounded wait may last
 };
 
 // Ordered compaction of per-tile flags (list[i] = flags of tile lo+i) into the visited list:

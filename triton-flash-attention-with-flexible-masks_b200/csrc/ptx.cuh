@@ -18,6 +18,9 @@ enum : int {
     ST_WAIT_TIMEOUT = 100,     // + role id (see the kernels): a bounded mbarrier wait ran out
     ST_ID_RANGE = 200,         // a negative query id does not fit in int32
 };
+// A time-out leaves the device in an unknown state: every later launch refuses to compute until the
+// host has read and cleared the word. An id out of range only concerns the call that passed it.
+__device__ __forceinline__ bool status_is_fatal(int s) { return s >= ST_WAIT_TIMEOUT && s < ST_ID_RANGE; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -68,13 +71,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Limit of one wait, in SM clocks (~0.25 s at 2 GHz). No legitimate wait in these kernels
-// lasts longer than a few tile times (microseconds).
+// Default limit of one wait, in SM clocks (~0.25 s at 2 GHz). No legitimate wait in these kernels
+// lasts longer than a few tile times (microseconds), but a CTA that is time-sliced out (another
+// context on the GPU, a profiler replay) sees the clock run on: hosts that share a GPU between
+// contexts can raise the limit (FA_B200_WAIT_LIMIT_CLOCKS, read by the library when it is loaded).
 constexpr long long kWaitLimitClocks = 500LL * 1000 * 1000;
 
 struct Abort {
     volatile int* flag;  // shared memory, one per CTA
     int* status;         // global status word
+    long long limit;     // SM clocks one wait may last
 };
 
 // Returns false when the wait was abandoned (limit reached here, or another role gave up).
@@ -86,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 31u) == 0u) {
             if (*ab.flag) return false;
-            if (clock64() - t0 > kWaitLimitClocks) {
+            if (clock64() - t0 > ab.limit) {
                 *ab.flag = 1;
                 atomicCAS(ab.status, 0, code);
                 return false;

@@ -61,8 +61,18 @@ def _status_word(device):
 
 
 def check_status(device=None):
-    """Synchronises `device` and raises if a kernel recorded an error since the last check."""
-    devs = list(_STATUS) if device is None else [torch.device(device).index or 0]
+    """Synchronises `device` (default: every device used so far) and raises if a kernel recorded an
+    error since the last check. A device given without an index means the current device.
+
+    The status word of a device is sticky: once a bounded wait inside a kernel has run out, every
+    later attention kernel on that device returns at once and fills its outputs with NaN, until this
+    function has been called (it clears the word). Call it once per step, or set
+    FA_B200_SYNC_STATUS=1 to have every forward and backward call do so."""
+    if device is None:
+        devs = list(_STATUS)
+    else:
+        idx = torch.device(device).index
+        devs = [torch.cuda.current_device() if idx is None else idx]
     for idx in devs:
         st = _STATUS.get(idx)
         if st is None:
@@ -87,6 +97,15 @@ def maybe_contiguous(x):
             if size > 1 and (stride <= 0 or stride % 8 != 0):
                 ok = False
     return x if ok else x.contiguous()
+
+
+def _same_device(ref, **tensors):
+    """Every pointer handed to the library is dereferenced on ref's device: a tensor that lives elsewhere
+    (host memory, another GPU) must be refused here, before any launch."""
+    for name, t in tensors.items():
+        if t is not None and t.device != ref.device:
+            raise ValueError(f"flash_b200: {name} is on {t.device}, but q is on {ref.device}; all tensors of a call "
+                             "must be on the same CUDA device")
 
 
 def _tensor(x):
@@ -173,6 +192,9 @@ class FlashAttention(torch.autograd.Function):
         assert score_func_mode in (SCORE_FUNC_MODE0_NOPE, SCORE_FUNC_MODE1_DOC)
         if not q.is_cuda:
             raise RuntimeError("flash_b200 runs on CUDA tensors only (there is no CPU implementation)")
+        _same_device(q, k=k, v=v, eq=eq, ek=ek)
+        if k.dtype != q.dtype or v.dtype != q.dtype:
+            raise ValueError(f"flash_b200: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
         if D not in (64, 128):
             raise NotImplementedError(f"flash_b200 implements head dims 64 and 128, got {D}")
         if sm_scale is None:
@@ -228,6 +250,9 @@ class FlashAttention(torch.autograd.Function):
         B, H, M, D, N, Hk, num_groups, MN_GAP = ctx.shapes
         score_func_mode, = ctx.score_func_info
         plan = ctx.plan
+        _same_device(q, do=do)
+        if do.dtype != q.dtype:
+            do = do.to(q.dtype)
         do = maybe_contiguous(do)
         with torch.cuda.device(q.device):
             prob = _problem(B, H, Hk, M, N, D, q.dtype, causal, score_func_mode, ctx.id_heads, sm_scale)
@@ -310,6 +335,13 @@ def debug_mask(B, H, M, N, causal, eq=None, ek=None, score_func_mode=SCORE_FUNC_
     tile_class [B,He,nQ,nK] uint8) computed on the device by the attention kernels' own predicate."""
     lib = _lib.load()
     device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("flash_b200 runs on CUDA devices only (there is no CPU implementation)")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    for name, t in (("eq", eq), ("ek", ek)):
+        if t is not None and t.device != device:
+            raise ValueError(f"flash_b200: {name} is on {t.device}, but the mask is evaluated on {device}")
     id_heads = 1
     with torch.cuda.device(device):
         status = _status_word(device)

@@ -1,6 +1,6 @@
 """Seeded synthetic inputs with the shapes and id distributions of the five benchmark
 configurations (they stand in for the reference's own benchmark inputs, testing.py:110-120 and
-:270-284; no dataset is involved). Used by the tests, the golden-vector script and bench.py.
+:270-284; no dataset is involved). Used by the tests, the golden-vector script and the benchmark.
 
 Ids are int64 `[B, H, L]` views with head stride 0 (`expand`), as the reference's sampler
 produces them (testing.py:118). Documents get distinct negative ids (attend inside the document
@@ -39,8 +39,9 @@ def _round_to_sum(weights, total, minimum=1):
     return base + minimum
 
 
-def doc_ids(name, rng, B=None, L=None):
-    """(eq, ek) numpy int64 arrays [B, Lq], [B, Lk] for configuration `name`."""
+def doc_ids(name, rng, B=None, L=None, always_attend=0.0):
+    """(eq, ek) numpy int64 arrays [B, Lq], [B, Lk] for configuration `name`. `always_attend` > 0 overwrites
+    that fraction of the positions of configuration 1 with an id >= 0, as configuration 0 does."""
     cfg = CONFIGS[name]
     B = B or cfg["B"]
     if name == "c0":
@@ -59,7 +60,10 @@ def doc_ids(name, rng, B=None, L=None):
         for _ in range(B):
             ndoc = int(rng.integers(1, 17))
             lengths = _round_to_sum(rng.dirichlet(np.ones(ndoc)), L)
-            out.append(_ids_from_lengths(lengths))
+            ids = _ids_from_lengths(lengths)
+            if always_attend > 0:
+                ids[rng.random(L) < always_attend] = 1
+            out.append(ids)
         e = np.stack(out)
         return e, e
     if name == "c2":
@@ -78,18 +82,20 @@ def doc_ids(name, rng, B=None, L=None):
     return None, None
 
 
-def make_inputs(name, device="cpu", B=None, H=None, dtype=None, with_do=True):
+def make_inputs(name, device="cpu", B=None, H=None, dtype=None, with_do=True, seed=None, always_attend=0.0):
     """Tensors of configuration `name` (optionally fewer batches / heads, same per-head
-    distribution). Returns dict(q, k, v, do, eq, ek, causal, mode, sm_scale, cfg)."""
+    distribution; `seed` replaces the configuration's own). Returns dict(q, k, v, do, eq, ek, causal, mode,
+    sm_scale, cfg)."""
     cfg = dict(CONFIGS[name])
     if B is not None:
         cfg["B"] = B
     if H is not None:
         cfg["H"] = cfg["Hk"] = H
     tdtype = dtype or TORCH_DTYPES[cfg["dtype"]]
-    rng = np.random.default_rng(SEEDS[name])
-    eq_np, ek_np = doc_ids(name, rng, B=cfg["B"])
-    gen = torch.Generator(device=device).manual_seed(SEEDS[name])
+    seed = SEEDS[name] if seed is None else seed
+    rng = np.random.default_rng(seed)
+    eq_np, ek_np = doc_ids(name, rng, B=cfg["B"], always_attend=always_attend)
+    gen = torch.Generator(device=device).manual_seed(seed)
     shp_q = (cfg["B"], cfg["H"], cfg["M"], cfg["D"])
     shp_k = (cfg["B"], cfg["Hk"], cfg["N"], cfg["D"])
 
