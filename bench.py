@@ -10,8 +10,10 @@ torchrun, one process per GPU) the 32 heads are split over the ranks, with no co
 the operator; the step time is the maximum over ranks. The metric is effective TFLOP/s:
 14 * D * nnz per step, nnz = number of unmasked score entries (4*D*nnz forward, 10*D*nnz backward).
 
-`--impl reference` times the reference's CPU masked-attention computation (its restatement in
-oracle/attention_oracle.py, fp32 torch on the host cores) on a bounded sample of the same workload.
+`--impl reference` times the reference's CPU masked-attention computation on a bounded sample of the
+same workload, fp32 torch on all host cores: the reference's own `_attn_torch` (testing.py:32-47) when
+the environment variable FA_REFERENCE names a checkout of the reference, else its restatement in
+oracle/attention_oracle.py.
 
 Prints ONE JSON line on rank 0.
 """
@@ -24,14 +26,16 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "triton-flash-attention-with-flexible-masks_b200"))
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 import numpy as np
 import torch
 
 from flash_b200 import workloads
 
-METRIC = "effective attention TFLOP/s fwd+bwd (doc-masked bf16)"
+def metric_name(cfg, backward):
+    """BASELINE's metric, labelled with what the workload really is."""
+    what = "doc-masked" if cfg["mode"] else ("causal, no id mask" if cfg["causal"] else "no mask")
+    return f"effective attention TFLOP/s {'fwd+bwd' if backward else 'fwd'} ({what} {cfg['dtype']})"
 # algorithmic FLOPs per unmasked entry, in units of D: S and P*V forward; S, dP, dV, dK in the
 # dK/dV kernel; dQ (the dQ kernel's recomputation of S and dP is not algorithmic work)
 FLOPS_PER_ENTRY = {"fwd": 4, "dkdv": 8, "dq": 2}
@@ -117,11 +121,51 @@ def dist_env():
 # ------------------------------------------------------------------------------------------
 # CPU leg: the reference's masked-attention computation on the host cores, bounded sample
 # ------------------------------------------------------------------------------------------
+def reference_attn_torch():
+    """The reference's own `_attn_torch` (testing.py:32-47) if FA_REFERENCE names a checkout of it, else None.
+    testing.py probes the GPU's compute capability when it is imported (testing.py:22); on a host without a
+    driver that probe is answered here, nothing else of the module is touched."""
+    ref = os.environ.get("FA_REFERENCE")
+    if not ref or not os.path.isfile(os.path.join(ref, "testing.py")):
+        return None
+    try:
+        if not torch.cuda.is_available():
+            torch.cuda.get_device_capability = lambda *a, **k: (10, 0)
+        sys.path.insert(0, ref)
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):  # the module prints when imported; stdout carries one JSON line only
+            import testing as ref_testing
+        return ref_testing._attn_torch
+    except Exception as exc:  # the checkout is there but does not import: say so and use the port
+        print(f"[bench] FA_REFERENCE={ref} could not be imported ({exc!r}); timing the port", file=sys.stderr)
+        return None
+
+
+def one_head_with_reference(attn_torch, q, k, v, do, causal, eq, ek, mode, chunk):
+    """Forward + backward of one (batch, head) through the reference's `_attn_torch`, in query chunks so that
+    the explicit score matrix stays chunk x N (rows [s, e) against keys [0, e) keep its bottom-right causal
+    alignment exact); the mask is the one the reference's sampler builds (testing.py:114)."""
+    M, N = q.shape[0], k.shape[0]
+    gap = max(0, N - M)
+    kf, vf = k.clone().requires_grad_(), v.clone().requires_grad_()
+    for s0 in range(0, M, chunk):
+        s1 = min(M, s0 + chunk)
+        n_hi = min(N, s1 + gap) if causal else N
+        qc = q[s0:s1].clone().requires_grad_()
+        mask = None
+        if mode == 1:
+            mask = (eq[s0:s1].unsqueeze(-1) >= 0) | (eq[s0:s1].unsqueeze(-1) == ek[:n_hi].unsqueeze(-2))
+        o = attn_torch(qc[None, None], kf[None, None, :n_hi], vf[None, None, :n_hi], causal, attn_mask=mask)
+        o.backward(do[None, None, s0:s1])
+
+
 def cpu_sample(name, steps=1, warmup=0, rows=None):
     """Times forward+backward of ONE (batch, head) of the workload (all its query rows unless `rows`
     limits it to the last ones), fp32, all host threads: 1/(B*H) of a step."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import attention_oracle as orc
+    # torchrun exports OMP_NUM_THREADS=1 to its workers: the CPU leg uses every core it can get
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cfg = workloads.CONFIGS[name]
     M, N, D = cfg["M"], cfg["N"], cfg["D"]
     rng = np.random.default_rng(workloads.SEEDS[name])
@@ -137,17 +181,24 @@ def cpu_sample(name, steps=1, warmup=0, rows=None):
     # rows M-rows..M-1 of an M x N causal problem == a rows x N problem with the same bottom-right alignment
     nnz = orc.count_unmasked(rows, N, cfg["causal"], None if eq is None else eq.numpy(),
                              None if ek is None else ek.numpy(), cfg["mode"])
+    attn_torch = reference_attn_torch()
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        orc.attention_one_head_chunked(q, k, v, do, cfg["causal"], 1.0 / np.sqrt(D), eq, ek, cfg["mode"], chunk=512)
+        if attn_torch is not None:
+            one_head_with_reference(attn_torch, q, k, v, do, cfg["causal"], eq, ek, cfg["mode"], chunk=512)
+        else:
+            orc.attention_one_head_chunked(q, k, v, do, cfg["causal"], 1.0 / np.sqrt(D), eq, ek, cfg["mode"], chunk=512)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
-    sec = float(np.mean(times))
+    sec = float(np.median(times))
     flops = 14.0 * D * nnz
-    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{name}: one of the {cfg['B'] * cfg['H']} (batch, head) pairs, {rows} query rows x {N} keys, fwd+bwd, fp32 torch on CPU, "
+    kind = "reference" if attn_torch is not None else "port"
+    how = "the reference's own _attn_torch" if kind == "reference" else "oracle port of the reference's _attn_torch"
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{name}: one of the {cfg['B'] * cfg['H']} (batch, head) pairs, {rows} query rows x {N} keys, fwd+bwd, fp32 torch on CPU "
+                      f"({how}, query chunks of 512), "
                       f"{sec * 1e3:.0f} ms per pass, nnz={nnz}",
             "ms_per_step": sec * 1e3}
 
@@ -158,7 +209,7 @@ def run_reference(args):
         return
     r = cpu_sample(args.workload, steps=args.steps, warmup=args.warmup)
     cfg = workloads.CONFIGS[args.workload]
-    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+    line = {"impl": "reference", "metric": metric_name(cfg, True), "value": r["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(args.workload, cfg), "sample": r["sample"]},
@@ -176,6 +227,50 @@ def workload_name(name, cfg):
 # ------------------------------------------------------------------------------------------
 # GPU leg
 # ------------------------------------------------------------------------------------------
+def percentile(xs, q):
+    return float(np.percentile(np.asarray(xs, dtype=np.float64), q))
+
+
+def validate_shards(shard, w, outs, dim, world, rank, backward):
+    """After the timed region: the first head (or batch entry) of every rank's shard is gathered with NCCL
+    (inputs and results) and rank 0 checks each against the CPU oracle in query chunks. Returns None on the
+    other ranks, else dict(ok, cases, max_abs)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import attention_oracle as orc
+    names = ("q", "k", "v", "do", "o", "dq", "dk", "dv") if backward else ("q", "k", "v", "o")
+    local = dict(w, **outs)
+    sel = (lambda x: x[:, :1]) if dim == 1 else (lambda x: x[:1, :1])
+    got = {}
+    for n in names:
+        x = sel(local[n]).detach().contiguous()
+        got[n] = shard.gather_shards(x, dim) if world > 1 else x
+    if rank != 0:
+        return None
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    cfg = w["cfg"]
+    worst = {}
+    ok = True
+    for r in range(world):
+        pick = (lambda x: x[0, r]) if dim == 1 else (lambda x: x[r, 0])
+        b = 0 if dim == 1 else 0  # ids are generated alike for every rank's shard (same seed): entry 0
+        eq = torch.from_numpy(w["eq_np"][b]) if w["eq_np"] is not None else None
+        ek = torch.from_numpy(w["ek_np"][b]) if w["ek_np"] is not None else None
+        ref = orc.attention_one_head_chunked(pick(got["q"]).cpu(), pick(got["k"]).cpu(), pick(got["v"]).cpu(),
+                                             pick(got["do"]).cpu() if backward else None, w["causal"], w["sm_scale"],
+                                             eq, ek, w["mode"], chunk=2048, backward=backward)
+        for n, want in zip(("o", "dq", "dk", "dv"), ref):
+            if want is None:
+                continue
+            have = pick(got[n]).float().cpu()
+            err = (have - want).abs()
+            bound = torch.full_like(want, 2e-2)
+            if have.dtype == torch.float32 and cfg["dtype"] == "bf16":
+                bound = torch.where(want.abs() < 2.56, bound, want.abs() * 2.0 ** -7)  # bf16 cannot be closer there
+            worst[n] = max(worst.get(n, 0.0), float(err.max()))
+            ok = ok and bool(torch.isfinite(have).all()) and bool((err <= bound).all())
+    return {"ok": ok, "cases": world, "max_abs": worst}
+
+
 def run_ours(args):
     import torch.distributed as dist
     import flash_b200 as fb
@@ -195,29 +290,12 @@ def run_ours(args):
         cfg["B"] = args.batch
     if args.heads:
         cfg["H"] = cfg["Hk"] = args.heads
-    dim, qs, _ = shard.shard_slices(cfg["B"], cfg["H"], cfg["Hk"], world, rank)
+    # configuration 4 is sharded by batch, the document-masked ones by head (as the benchmark configurations say)
+    dim, qs, _ = shard.shard_slices(cfg["B"], cfg["H"], cfg["Hk"], world, rank, prefer="batch" if name == "c4" else "heads")
     n_local = len(range(*qs.indices(cfg["H"] if dim == 1 else cfg["B"])))
     kw = {"H": n_local, "B": cfg["B"]} if dim == 1 else {"B": n_local, "H": cfg["H"]}
-    w = workloads.make_inputs(name, device=dev, **kw)          # this rank's shard, same ids on every rank
-    per_b = nnz_per_head(w)
-    # equal shards with the same ids on every rank
-    nnz_local = sum(per_b) * (n_local if dim == 1 else cfg["H"])
-    nnz_total = nnz_local * world
     D = cfg["D"]
-    backward = not args.forward_only and w["do"] is not None
-    flops_step_local = (14.0 if backward else 4.0) * D * nnz_local
-    flops_step_total = flops_step_local * world  # equal shards
-
-    q, k, v = [w[x].requires_grad_(backward) for x in "qkv"]
-    att = (w["causal"], w["sm_scale"], w["eq"], w["ek"], w["mode"])
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.int8, device=dev)
-
-    def step():
-        o = fb.attention(q, k, v, *att)
-        if backward:
-            o.backward(w["do"])
-            q.grad = k.grad = v.grad = None
-        return o
 
     def barrier():
         torch.cuda.synchronize()
@@ -225,97 +303,123 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    # The timed step is one CUDA graph of the step's calls (plan, forward, backward): a rank's share of
-    # the step is short (0.5 ms at 8 GPUs) and Python enqueues it more slowly than the GPU runs it when
-    # the host is busy, which a graph replay does not depend on. With one rank the per-kernel events
-    # are captured into the timed graph as event-record nodes and read after every timed replay.
-    # They cost about 4 us each, too much for the short steps of several ranks: there the timed graph
-    # has none and the per-kernel times come from one replay of a second graph (with the events) right
-    # after the timed region. --no-graph times plain eager calls (every step carries its own events).
-    use_graph = not args.no_graph
-    for _ in range(args.warmup):
-        flush.zero_()
-        step()
-    barrier()
-    graph = None
-    launches_per_step = 0
-    prof_graph = None
-    if use_graph:
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step()
-            torch.cuda.current_stream().wait_stream(side)
-            graph_prof = torch.cuda.CUDAGraph()
-            ops.PROFILE = []
-            l0 = ops.LAUNCHES
-            with torch.cuda.graph(graph_prof):
-                step()
-            launches_per_step = ops.LAUNCHES - l0
-            prof_graph, ops.PROFILE = ops.PROFILE, None
-            graph = graph_prof
-            if world > 1:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    step()
-            graph.replay()
-            torch.cuda.synchronize()
-            fb.check_status()
-        except Exception as exc:  # capture refused: time eager steps instead
-            print(f"[bench] CUDA graph capture failed ({exc}); timing eager steps", file=sys.stderr)
-            graph, ops.PROFILE = None, None
-            torch.cuda.synchronize()
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    if graph is None:
-        ops.PROFILE = []
-    launches0 = ops.LAUNCHES
-    evs = []
-    kern_acc = {}
-    for _ in range(args.steps):
-        flush.zero_()  # L2 flush between timed iterations (not timed)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        if graph is not None:
-            graph.replay()
-        else:
-            step()
-        e1.record()
-        evs.append((e0, e1))
-        if graph is not None and graph is graph_prof:
-            # the graph's event nodes are re-recorded by every replay: read this step's kernel times now
-            torch.cuda.synchronize()
-            for nm, a, c in prof_graph:
-                kern_acc.setdefault(nm, []).append(a.elapsed_time(c))
-    barrier()
-    clocks = sampler.stop()
-    if graph is None:
-        prof, ops.PROFILE = ops.PROFILE, None
-        launches = ops.LAUNCHES - launches0
-    else:
-        if graph is not graph_prof:  # several ranks: one replay of the graph that holds the per-kernel events
-            flush.zero_()
-            graph_prof.replay()
-            torch.cuda.synchronize()
-        prof = prof_graph  # as recorded by the last replay of the graph that holds them
-        launches = launches_per_step * args.steps
-    fb.check_status()
-    total_ms = sum(a.elapsed_time(b) for a, b in evs)
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    value = flops_step_total / (ms_per_step * 1e-3) / 1e12
+    def measure(seed, steps, warmup, sample_clocks):
+        """Times `steps` steps of the workload drawn with `seed` on this rank's shard. Every rank draws the same ids
+        (equal work) but its own q, k, v, dO. Returns a dict with the per-step times (max over ranks) and the
+        per-kernel times of this rank."""
+        w = workloads.make_inputs(name, device=dev, seed=seed, data_seed=1000 * seed + rank, **kw)
+        per_b = nnz_per_head(w)
+        nnz_local = sum(per_b) * (n_local if dim == 1 else cfg["H"])
+        backward = not args.forward_only and w["do"] is not None
+        q, k, v = [w[x].requires_grad_(backward) for x in "qkv"]
+        att = (w["causal"], w["sm_scale"], w["eq"], w["ek"], w["mode"])
+        outs = {}
 
-    # per-kernel durations measured live in the timed region (events on the launching stream)
-    kern = kern_acc
-    if not kern:
-        for nm, a, b in prof:
-            kern.setdefault(nm, []).append(a.elapsed_time(b))
-    kern_ms = {nm: float(np.mean(x)) for nm, x in kern.items()}
+        def step(keep=False):
+            o = fb.attention(q, k, v, *att)
+            if backward:
+                o.backward(w["do"])
+                if keep:
+                    outs.update(o=o.detach(), dq=q.grad, dk=k.grad, dv=v.grad)
+                q.grad = k.grad = v.grad = None
+            elif keep:
+                outs.update(o=o.detach())
+            return o
+
+        # The timed step is one CUDA graph of the step's calls (plan, forward, backward): a rank's share of
+        # the step is short (0.5 ms at 8 GPUs) and Python enqueues it more slowly than the GPU runs it when
+        # the host is busy, which a graph replay does not depend on. With one rank the per-kernel events
+        # are captured into the timed graph as event-record nodes and read after every timed replay.
+        # They cost about 4 us each, too much for the short steps of several ranks: there the timed graph
+        # has none and the per-kernel times come from one replay of a second graph (with the events) right
+        # after the timed region. --no-graph times plain eager calls (every step carries its own events).
+        for _ in range(warmup):
+            flush.zero_()
+            step()
+        barrier()
+        graph = graph_prof = prof_graph = None
+        launches_per_step = 0
+        if not args.no_graph:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step()
+                torch.cuda.current_stream().wait_stream(side)
+                graph_prof = torch.cuda.CUDAGraph()
+                ops.PROFILE = []
+                l0 = ops.LAUNCHES
+                with torch.cuda.graph(graph_prof):
+                    step()
+                launches_per_step = ops.LAUNCHES - l0
+                prof_graph, ops.PROFILE = ops.PROFILE, None
+                graph = graph_prof
+                if world > 1:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        step()
+                graph.replay()
+                torch.cuda.synchronize()
+                fb.check_status()
+            except Exception as exc:  # capture refused: time eager steps instead
+                print(f"[bench] CUDA graph capture failed ({exc}); timing eager steps", file=sys.stderr)
+                graph, ops.PROFILE = None, None
+                torch.cuda.synchronize()
+        barrier()
+        sampler = ClockSampler(local) if sample_clocks else None
+        if sampler:
+            sampler.start()
+        if graph is None:
+            ops.PROFILE = []
+        launches0 = ops.LAUNCHES
+        evs, kern = [], {}
+        for _ in range(steps):
+            flush.zero_()  # L2 flush between timed iterations (not timed)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+            e1.record()
+            evs.append((e0, e1))
+            if graph is not None and graph is graph_prof:
+                # the graph's event nodes are re-recorded by every replay: read this step's kernel times now
+                torch.cuda.synchronize()
+                for nm, a, c in prof_graph:
+                    kern.setdefault(nm, []).append(a.elapsed_time(c))
+        barrier()
+        clocks = sampler.stop() if sampler else None
+        if graph is None:
+            prof, ops.PROFILE = ops.PROFILE, None
+            launches = ops.LAUNCHES - launches0
+        else:
+            if graph is not graph_prof:  # several ranks: one replay of the graph that holds the per-kernel events
+                flush.zero_()
+                graph_prof.replay()
+                torch.cuda.synchronize()
+            prof = prof_graph  # as recorded by the last replay of the graph that holds them
+            launches = launches_per_step * steps
+        fb.check_status()
+        if not kern:
+            for nm, a, c in prof:
+                kern.setdefault(nm, []).append(a.elapsed_time(c))
+        t = torch.tensor([a.elapsed_time(c) for a, c in evs], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every step counts with its slowest rank
+        return {"w": w, "ms": t.tolist(), "kern_ms": {nm: float(np.median(x)) for nm, x in kern.items()},
+                "nnz_local": nnz_local, "backward": backward, "launches": launches, "clocks": clocks,
+                "graph": graph is not None, "step": step, "outs": outs}
+
+    m = measure(workloads.SEEDS[name], args.steps, args.warmup, True)
+    w, backward, nnz_local = m["w"], m["backward"], m["nnz_local"]
+    nnz_total = nnz_local * world  # equal shards
+    flops_step_total = (14.0 if backward else 4.0) * D * nnz_total
+    # the headline is the median step (the reference's do_bench reports the median and the 20 % / 80 % quantiles,
+    # testing.py:152); the mean over the K timed steps is reported beside it
+    ms_per_step = percentile(m["ms"], 50)
+    value = flops_step_total / (ms_per_step * 1e-3) / 1e12
+    kern_ms = m["kern_ms"]
     peak_tf, peak_bw, peak_src = peaks()
     dom = max((nm for nm in kern_ms if nm in FLOPS_PER_ENTRY), key=lambda nm: kern_ms[nm])
     achieved = FLOPS_PER_ENTRY[dom] * D * nnz_local / (kern_ms[dom] * 1e-3) / 1e12
@@ -329,6 +433,38 @@ def run_ours(args):
                 "kernel_ms": kern_ms,
                 "per_kernel_tflops": {nm: FLOPS_PER_ENTRY[nm] * D * nnz_local / (kern_ms[nm] * 1e-3) / 1e12
                                       for nm in kern_ms if nm in FLOPS_PER_ENTRY}}
+    # the forward call alone (mask plan + forward kernel), this rank's share, as measured inside the timed steps
+    fwd_ms = kern_ms.get("fwd", 0.0) + kern_ms.get("plan", 0.0)
+    fwd = None
+    if fwd_ms > 0:
+        fv = 4.0 * D * nnz_local * world / (fwd_ms * 1e-3) / 1e12
+        fwd = {"value": fv, "unit": "TFLOP/s", "ms": fwd_ms, "frac_of_measured": fv / (peak_tf * world),
+               "frac_of_nominal": fv / (2250.0 * world),
+               "what": "forward call (mask plan + forward kernel) of rank 0's shard, from the per-kernel events of the timed steps"}
+
+    # other draws of the same configuration: the headline seed holds one very long document, which raises the
+    # unmasked fraction and the share of full tiles; seeds 0-2 are the ordinary case
+    other = None
+    if name == "c3" and not args.no_other_seeds:
+        other = {}
+        cfgw = w["cfg"]
+        for sd in (0, 1, 2):
+            mo = measure(sd, max(3, min(args.steps, 5)), 3, False)
+            ms_o = percentile(mo["ms"], 50)
+            tot = mo["nnz_local"] * world
+            dense_o = cfgw["B"] * cfg["H"] * cfgw["M"] * cfgw["N"] * 0.5
+            other[str(sd)] = {"value": (14.0 if backward else 4.0) * D * tot / (ms_o * 1e-3) / 1e12, "ms_per_step": ms_o,
+                              "unmasked_fraction_of_causal": tot / dense_o,
+                              "fwd_value": 4.0 * D * tot / ((mo["kern_ms"].get("fwd", 0) + mo["kern_ms"].get("plan", 0)) * 1e-3) / 1e12}
+            del mo
+
+    validation = None
+    if not args.no_validate:
+        m["step"](keep=True)
+        torch.cuda.synchronize()
+        validation = validate_shards(shard, w, m["outs"], dim, world, rank, backward)
+        m["outs"].clear()
+        barrier()
 
     # end to end through the public call for HOST buffers (flash_b200.attention_host): H2D of q, k, v, dO
     # and ids from pinned memory, forward + backward, D2H of O, dQ, dK, dV -- all inside the timed region
@@ -349,7 +485,7 @@ def run_ours(args):
             h2d += sum(t_.numel() * t_.element_size() for t_ in ids_host)
         d2h = sum(t_.numel() * t_.element_size() for t_ in host_out.values())
 
-        E2E_PARTS = 32  # one head per slice at c3: the step is bound by the copies, finer slices overlap them better
+        E2E_PARTS = 32  # slices of the shard: the step is bound by the copies, finer slices overlap them better
 
         def e2e_step():
             # the package's call for host tensors: slices of heads are copied in, computed and copied
@@ -393,14 +529,16 @@ def run_ours(args):
 
     if rank == 0:
         dense = cfg["B"] * cfg["H"] * cfg["M"] * cfg["N"] * (0.5 if cfg["causal"] else 1.0)
-        line = {"metric": METRIC if backward else METRIC.replace("fwd+bwd", "fwd"), "value": value, "unit": "TFLOP/s",
+        line = {"metric": metric_name(cfg, backward), "value": value, "unit": "TFLOP/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "ms_p20": percentile(m["ms"], 20), "ms_p80": percentile(m["ms"], 80), "ms_mean": float(np.mean(m["ms"])),
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"],
                 "data": "synthetic",
                 "config": {"workload": workload_name(name, cfg), "seed": workloads.SEEDS[name],
                            "sharding": f"{'heads' if dim == 1 else 'batches'} over {world} rank(s), {n_local} per rank",
                            "l2": "256 MiB buffer written between timed iterations",
-                           "timed_step": ("eager calls with per-kernel events" if graph is None else
+                           "statistic": "ms_per_step and value: median of the timed steps, each step taken at its slowest rank",
+                           "timed_step": ("eager calls with per-kernel events" if not m["graph"] else
                                           "one CUDA graph replay per step (plan, forward, backward); per-kernel events are nodes of "
                                           "the graph, read after every timed replay" if world == 1 else
                                           "one CUDA graph replay per step (plan, forward, backward); per-kernel times from one replay "
@@ -408,7 +546,9 @@ def run_ours(args):
                            "unmasked_fraction_of_causal": nnz_total / dense,
                            "dense_count_tflops": (14.0 if backward else 4.0) * D * dense / (ms_per_step * 1e-3) / 1e12},
                 "frac_of_measured_peak": value / (peak_tf * world), "frac_of_nominal_peak": value / (2250.0 * world),
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
+                "fwd": fwd, "other_seeds": other, "validated": None if validation is None else validation["ok"],
+                "validation": validation,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": m["launches"], "clocks": m["clocks"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -427,6 +567,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls instead of CUDA-graph replays of the step")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-other-seeds", action="store_true", help="skip the extra draws (seeds 0-2) of configuration 3")
+    ap.add_argument("--no-validate", action="store_true", help="skip the check of the shards' results against the CPU oracle")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -65,3 +65,48 @@ def test_shard_by_head_two_ranks():
 
 def test_shard_by_batch_two_ranks():
     _run("batch")
+
+
+def _failing_worker(rank, world, port, q_out):
+    """Rank 1 fails on the host between steps, with nothing in flight: it raises before the gather. Rank 0
+    learns of it when its next collective ends with an error after the (short) process-group timeout."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        x = torch.full((4,), float(rank))
+        dist.all_reduce(x)  # a first, healthy step
+        assert float(x[0]) == 1.0
+        if rank == 1:
+            raise RuntimeError("injected host-side failure of rank 1")
+        try:
+            shard.gather_shards(torch.zeros(1, 2, 8, 4), 1)
+            q_out.put((rank, "gather returned although a rank was missing"))
+        except Exception as exc:  # gloo reports the missing peer (connection closed or timed out)
+            q_out.put((rank, "noticed: " + type(exc).__name__))
+    except RuntimeError as exc:
+        if rank == 1:
+            q_out.put((rank, "raised: " + str(exc)))
+            return
+        raise
+    finally:
+        if rank == 0:
+            try:
+                dist.destroy_process_group()
+            except Exception:
+                pass
+
+
+def test_a_rank_that_fails_between_steps_is_noticed_by_the_others():
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q_out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q_out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert res[1].startswith("raised: injected")
+    assert res[0].startswith("noticed:"), res[0]

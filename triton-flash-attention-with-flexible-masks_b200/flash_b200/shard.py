@@ -8,20 +8,30 @@ import torch
 import torch.distributed as dist
 
 
-def shard_slices(B, H, Hk, world_size, rank):
+def shard_slices(B, H, Hk, world_size, rank, prefer="heads"):
     """Returns (dim, q_slice, kv_slice): the tensor dimension that is split (1 = heads,
     0 = batch) and this rank's slice of it for q-shaped and k/v-shaped tensors.
-    Heads are split when the kv heads divide evenly, otherwise batches."""
+    With prefer="heads" the kv heads are split when they divide evenly, otherwise the batches;
+    with prefer="batch" the other way round."""
     assert 0 <= rank < world_size
     assert H % Hk == 0
     G = H // Hk
-    if Hk % world_size == 0:
+
+    def by_heads():
         per = Hk // world_size
         return 1, slice(rank * per * G, (rank + 1) * per * G), slice(rank * per, (rank + 1) * per)
-    if B % world_size == 0:
+
+    def by_batch():
         per = B // world_size
         s = slice(rank * per, (rank + 1) * per)
         return 0, s, s
+
+    order = [(Hk, by_heads), (B, by_batch)]
+    if prefer == "batch":
+        order.reverse()
+    for extent, make in order:
+        if extent % world_size == 0:
+            return make()
     raise ValueError(f"cannot split B={B}, Hk={Hk} evenly over {world_size} ranks by head or by batch")
 
 

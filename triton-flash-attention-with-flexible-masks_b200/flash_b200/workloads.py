@@ -82,10 +82,11 @@ def doc_ids(name, rng, B=None, L=None, always_attend=0.0):
     return None, None
 
 
-def make_inputs(name, device="cpu", B=None, H=None, dtype=None, with_do=True, seed=None, always_attend=0.0):
+def make_inputs(name, device="cpu", B=None, H=None, dtype=None, with_do=True, seed=None, always_attend=0.0,
+                data_seed=None):
     """Tensors of configuration `name` (optionally fewer batches / heads, same per-head
-    distribution; `seed` replaces the configuration's own). Returns dict(q, k, v, do, eq, ek, causal, mode,
-    sm_scale, cfg)."""
+    distribution; `seed` replaces the configuration's own for the ids and, unless `data_seed` is given,
+    for q, k, v, dO). Returns dict(q, k, v, do, eq, ek, causal, mode, sm_scale, cfg)."""
     cfg = dict(CONFIGS[name])
     if B is not None:
         cfg["B"] = B
@@ -95,7 +96,7 @@ def make_inputs(name, device="cpu", B=None, H=None, dtype=None, with_do=True, se
     seed = SEEDS[name] if seed is None else seed
     rng = np.random.default_rng(seed)
     eq_np, ek_np = doc_ids(name, rng, B=cfg["B"], always_attend=always_attend)
-    gen = torch.Generator(device=device).manual_seed(seed)
+    gen = torch.Generator(device=device).manual_seed(seed if data_seed is None else data_seed)
     shp_q = (cfg["B"], cfg["H"], cfg["M"], cfg["D"])
     shp_k = (cfg["B"], cfg["Hk"], cfg["N"], cfg["D"])
 
