@@ -47,6 +47,7 @@ def pytest_terminal_summary(terminalreporter):
     tr.write_line("largest absolute errors against the fp32 reference evaluation (all / elements with |ref| < 2.56):")
     per_test = {}
     for (test, what), (a, b) in _ERRORS.items():
-        per_test.setdefault(test, []).append(f"{what.split()[-1] if ' ' in what else what} {a:.4f}/{b:.4f}")
+        fmt = (lambda x: f"{x:.4f}") if a >= 1e-3 else (lambda x: f"{x:.1e}")
+        per_test.setdefault(test, []).append(f"{what.split()[-1] if ' ' in what else what} {fmt(a)}/{fmt(b)}")
     for test, items in per_test.items():
         tr.write_line(f"  {test}: " + "  ".join(items[:12]) + (" ..." if len(items) > 12 else ""))

@@ -414,7 +414,7 @@ def test_unsupported_inputs_raise(fb):
     x = torch.zeros(1, 1, 64, 48, dtype=BF, device="cuda")
     with pytest.raises(AssertionError):  # the reference's own check on the head dim (flash_triton.py:512)
         fb.attention(x, x, x)
-    y = torch.zeros(1, 1, 64, 64, dtype=torch.float32, device="cuda")
+    y = torch.zeros(1, 1, 64, 64, dtype=torch.float64, device="cuda")
     with pytest.raises(NotImplementedError):
         fb.attention(y, y, y)
     z = torch.zeros(1, 1, 64, 64, dtype=BF, device="cuda")
@@ -525,4 +525,87 @@ def test_skipping_and_chunk_shortcuts_do_not_change_results(fb, monkeypatch):
     for a, b, name in zip(base, noskip, ("O", "dQ", "dK", "dV")):
         assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -6 * max(1.0, b.float().abs().max().item()), name
     monkeypatch.delenv("FA_B200_NO_SKIP")
+    fb.check_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# fp32 inputs (flash_triton.py:512, testing.py:158): fp32 kernels, max-abs 1e-4 against the fp32 evaluation
+# ---------------------------------------------------------------------------------------------
+TOL32 = 1e-4
+
+
+def close32(got, ref, what):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    err = (got - ref).abs().max().item()
+    import conftest
+    conftest.record_error(os.environ.get("PYTEST_CURRENT_TEST", "?").split("::")[-1].split(" ")[0], what, err, err)
+    assert err <= TOL32, f"{what}: max-abs error {err:.2e} > 1e-4"
+
+
+def test_config0_in_fp32_against_the_reference_fixture(fb):
+    """Benchmark configuration 0 in its own dtype: all of it, against the reference's `_attn_torch` outputs (and the
+    reference's Triton operator run by the interpreter), within 1e-4."""
+    z = np.load(os.path.join(GOLD, "c0.npz"))
+    w = workloads.make_inputs("c0", device="cpu")  # the fixture was computed on these CPU-generated inputs
+    assert w["q"].dtype == torch.float32
+    q, k, v = [w[x].cuda().requires_grad_() for x in "qkv"]
+    o = fb.attention(q, k, v, True, None, w["eq"].cuda(), w["ek"].cuda(), 1)
+    o.backward(w["do"].cuda())
+    sub = lambda x: x[:, :, ::8]
+    for which in ("ref", "tri"):
+        close32(sub(o), torch.from_numpy(z[f"{which}_o"]), f"c0 O vs {which}")
+        close32(sub(q.grad), torch.from_numpy(z[f"{which}_dq"]), f"c0 dQ vs {which}")
+        close32(sub(k.grad), torch.from_numpy(z[f"{which}_dk"]), f"c0 dK vs {which}")
+        close32(sub(v.grad), torch.from_numpy(z[f"{which}_dv"]), f"c0 dV vs {which}")
+    ro, rdq, rdk, rdv = orc.attention_forward_backward(w["q"], w["k"], w["v"], w["do"], True, None, w["eq"], w["ek"], 1)
+    close32(o, ro, "c0 O"); close32(q.grad, rdq, "c0 dQ"); close32(k.grad, rdk, "c0 dK"); close32(v.grad, rdv, "c0 dV")
+    fb.check_status()
+
+
+@pytest.mark.parametrize("case", [
+    # B, H, Hk, M, N, D, causal, mode, per_head
+    (1, 2, 2, 100, 200, 16, False, 0, False),
+    (2, 4, 2, 300, 430, 32, True, 1, False),
+    (1, 4, 1, 257, 257, 64, True, 1, True),
+    (1, 2, 2, 130, 1, 128, False, 0, False),
+    (2, 2, 2, 1, 300, 64, True, 1, False),
+    (1, 2, 1, 384, 1024, 128, False, 1, False),
+])
+def test_fp32_parity_with_oracle(fb, case):
+    B, H, Hk, M, N, D, causal, mode, per_head = case
+    rng = np.random.default_rng(D + M)
+    g = torch.Generator().manual_seed(D + N)
+    q = torch.randn(B, H, M, D, generator=g).cuda().requires_grad_()
+    k = torch.randn(B, Hk, N, D, generator=g).cuda().requires_grad_()
+    v = torch.randn(B, Hk, N, D, generator=g).cuda().requires_grad_()
+    do = torch.randn(B, H, M, D, generator=g).cuda()
+    eq = ek = None
+    if mode == 1:
+        ek = make_ids(B, H, N, 4, 0.04, rng, per_head)
+        eq = ek[..., torch.from_numpy(rng.integers(0, N, size=M))] if M != N else ek
+        eq, ek = eq.cuda(), ek.cuda()
+    o = fb.attention(q, k, v, causal, None, eq, ek, mode)
+    o.backward(do)
+    ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(), causal, None,
+                                                       None if eq is None else eq.cpu(), None if ek is None else ek.cpu(), mode)
+    close32(o, ro, "O"); close32(q.grad, rdq, "dQ"); close32(k.grad, rdk, "dK"); close32(v.grad, rdv, "dV")
+    fb.check_status()
+
+
+def test_fp32_strided_and_fully_masked_rows(fb):
+    B, H, L, D = 2, 3, 200, 64
+    g = torch.Generator().manual_seed(9)
+    base = [torch.randn(B, L, H, D, generator=g).cuda() for _ in range(4)]
+    q, k, v, do = [x.transpose(1, 2) for x in base]  # [B, H, L, D] views of [B, L, H, D] storage
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    ek = torch.full((B, 1, L), -1, dtype=torch.int64); ek[..., 90:] = -2
+    eq = ek.clone(); eq[..., 7] = -50  # a query whose id matches no key: zero row, zero gradients
+    eqx, ekx = eq.expand(B, H, L).cuda(), ek.expand(B, H, L).cuda()
+    o = fb.attention(q, k, v, False, 0.3, eqx, ekx, 1)
+    o.backward(do)
+    assert torch.all(o[:, :, 7] == 0) and torch.all(q.grad[:, :, 7] == 0)
+    ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(), False, 0.3,
+                                                       eqx.cpu(), ekx.cpu(), 1)
+    close32(o, ro, "O"); close32(q.grad, rdq, "dQ"); close32(k.grad, rdk, "dK"); close32(v.grad, rdv, "dV")
     fb.check_status()

@@ -18,6 +18,9 @@ cudaError_t launch_bwd_dkdv(int, bool, const CUtensorMap&, const CUtensorMap&, c
                             cudaStream_t);
 cudaError_t launch_bwd_dq(int, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
                           const CUtensorMap&, const CUtensorMap&, const DqParams&, int, cudaStream_t);
+
+// fp32 path (attn_f32.cu)
+cudaError_t launch_f32(int which, int D, const F32Params& p, cudaStream_t stream);
 }  // namespace fa
 
 namespace {
@@ -48,8 +51,12 @@ int check_problem(const fa_problem* p) {
     if (p->mode != FA_MODE0_NOPE && p->mode != FA_MODE1_DOC) return FA_ERR_BAD_ARG;
     if (p->id_heads != 1 && p->id_heads != p->H) return FA_ERR_BAD_ARG;
     if (p->causal && p->N < p->M) return FA_ERR_BAD_ARG;  // flash_triton.py:520
-    if (p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
-    if (p->dtype != FA_BF16 && p->dtype != FA_FP16) return FA_ERR_UNSUPPORTED;
+    if (p->dtype == FA_FP32) {  // fp32 FMA kernels: every head dim of the reference (flash_triton.py:512)
+        if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
+    } else {
+        if (p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
+        if (p->dtype != FA_BF16 && p->dtype != FA_FP16) return FA_ERR_UNSUPPORTED;
+    }
     if (!(p->sm_scale > 0.f)) return FA_ERR_UNSUPPORTED;
     if (fa::cdiv(p->N, fa::kBlk) > fa::kListCap || fa::cdiv(p->M, fa::kBlk) > fa::kListCap)
         return FA_ERR_UNSUPPORTED;  // at most 1024 blocks (131072 tokens) per sequence
@@ -66,6 +73,22 @@ int check_tensor(const fa_tensor* t, int B, int H, int L) {
         if (ext[i] > 1 && (t->stride[i] <= 0 || t->stride[i] % 8 != 0)) return FA_ERR_ALIGNMENT;
     }
     return FA_OK;
+}
+
+// fp32 tensors are read and written with plain loads and stores: 4-byte aligned base, last stride 1
+int check_tensor_f32(const fa_tensor* t, int B, int H, int L) {
+    if (!t || !t->ptr) return FA_ERR_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(t->ptr) % 4 != 0) return FA_ERR_ALIGNMENT;
+    if (t->stride[3] != 1) return FA_ERR_ALIGNMENT;
+    const int ext[3] = {B, H, L};
+    for (int i = 0; i < 3; ++i) {
+        if (ext[i] > 1 && t->stride[i] <= 0) return FA_ERR_ALIGNMENT;
+    }
+    return FA_OK;
+}
+
+fa::F32Tensor f32_view(const fa_tensor* t) {
+    return fa::F32Tensor{static_cast<float*>(t->ptr), t->stride[0], t->stride[1], t->stride[2]};
 }
 
 // 4-D map over [B, H, L, D]; box = 64 elements of D x 128 rows of L; 128-byte swizzle; rows
@@ -172,6 +195,30 @@ int sm_count() {
     return cached[dev];
 }
 
+// fp32 inputs: which = 0 forward, 1 delta, 2 dK / dV, 3 dQ; absent tensors are null
+int run_f32(int which, const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa_tensor* v, const fa_tensor* o,
+            const fa_tensor* d_o, const fa_tensor* dq, const fa_tensor* dk, const fa_tensor* dv, float* lse, float* delta,
+            const void* plan, void* stream) {
+    int rc;
+    fa::F32Params fp{};
+    const struct { const fa_tensor* t; fa::F32Tensor* dst; int H, L; } all[8] = {
+        {q, &fp.q, p->H, p->M}, {k, &fp.k, p->Hk, p->N}, {v, &fp.v, p->Hk, p->N}, {o, &fp.o, p->H, p->M},
+        {d_o, &fp.d_o, p->H, p->M}, {dq, &fp.dq, p->H, p->M}, {dk, &fp.dk, p->Hk, p->N}, {dv, &fp.dv, p->Hk, p->N}};
+    for (const auto& a : all) {
+        if (!a.t) continue;
+        if ((rc = check_tensor_f32(a.t, p->B, a.H, a.L))) return rc;
+        *a.dst = f32_view(a.t);
+    }
+    fa_problem pm = *p;
+    if (which == 1) pm.mode = FA_MODE0_NOPE;  // the row sums do not depend on the mask (and take no plan)
+    if ((rc = make_mask(&fp.mask, &pm, plan))) return rc;
+    fp.lse = lse;
+    fp.delta = delta;
+    fp.B = p->B; fp.H = p->H; fp.Hk = p->Hk; fp.G = p->H / p->Hk;
+    fp.scale = p->sm_scale;
+    return fa::launch_f32(which, p->D, fp, static_cast<cudaStream_t>(stream)) == cudaSuccess ? FA_OK : FA_ERR_LAUNCH;
+}
+
 }  // namespace
 
 extern "C" {
@@ -183,8 +230,8 @@ const char* fa_error_string(int code) {
         case FA_OK: return "ok";
         case FA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, H % Hk != 0, causal with N < M)";
         case FA_ERR_UNSUPPORTED:
-            return "unsupported problem (head dim must be 64 or 128, dtype bf16/fp16, sm_scale > 0, "
-                   "at most 131072 tokens per sequence)";
+            return "unsupported problem (head dim must be 64 or 128 for bf16/fp16 and 16, 32, 64 or 128 for fp32, "
+                   "sm_scale > 0, at most 131072 tokens per sequence)";
         case FA_ERR_ALIGNMENT:
             return "a buffer breaks the alignment rules (tensors: 16-byte aligned base, last stride 1, other strides "
                    "multiples of 8; lse, delta and plan: 16-byte aligned)";
@@ -242,6 +289,7 @@ int fa_fwd(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const fa
     if (rc) return rc;
     if (!lse || !status) return FA_ERR_BAD_ARG;
     if (!aligned16(lse)) return FA_ERR_ALIGNMENT;
+    if (p->dtype == FA_FP32) return run_f32(0, p, q, k, v, o, nullptr, nullptr, nullptr, nullptr, lse, nullptr, plan, stream);
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
     if ((rc = check_tensor(v, p->B, p->Hk, p->N))) return rc;
@@ -274,6 +322,8 @@ int fa_bwd_delta(const fa_problem* p, const fa_tensor* o, const fa_tensor* d_o, 
     if (rc) return rc;
     if (!delta) return FA_ERR_BAD_ARG;
     if (!aligned16(delta)) return FA_ERR_ALIGNMENT;
+    if (p->dtype == FA_FP32)
+        return run_f32(1, p, nullptr, nullptr, nullptr, o, d_o, nullptr, nullptr, nullptr, nullptr, delta, nullptr, stream);
     if ((rc = check_tensor(o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     fa::DeltaParams dp;
@@ -294,6 +344,8 @@ int fa_bwd_dkdv(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, con
     if (rc) return rc;
     if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
     if (!aligned16(lse) || !aligned16(delta)) return FA_ERR_ALIGNMENT;  // read with bulk copies
+    if (p->dtype == FA_FP32)
+        return run_f32(2, p, q, k, v, nullptr, d_o, nullptr, dk, dv, const_cast<float*>(lse), const_cast<float*>(delta), plan, stream);
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(k, p->B, p->Hk, p->N))) return rc;
@@ -337,6 +389,8 @@ int fa_bwd_dq(const fa_problem* p, const fa_tensor* q, const fa_tensor* k, const
     if (rc) return rc;
     if (!lse || !delta || !status) return FA_ERR_BAD_ARG;
     if (!aligned16(lse) || !aligned16(delta)) return FA_ERR_ALIGNMENT;  // read with bulk copies
+    if (p->dtype == FA_FP32)
+        return run_f32(3, p, q, k, v, nullptr, d_o, dq, nullptr, nullptr, const_cast<float*>(lse), const_cast<float*>(delta), plan, stream);
     if ((rc = check_tensor(q, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(d_o, p->B, p->H, p->M))) return rc;
     if ((rc = check_tensor(dq, p->B, p->H, p->M))) return rc;

@@ -50,6 +50,21 @@ struct DqParams {
     long long wait_limit;  // SM clocks a bounded wait may last
 };
 
+// fp32 kernels (attn_f32.cu): plain pointers and element strides, no tensor maps
+struct F32Tensor {
+    float* ptr;
+    int64_t sb, sh, sl;  // element strides; the D stride is 1
+};
+
+struct F32Params {
+    F32Tensor q, k, v, o, d_o, dq, dk, dv;
+    float* lse;    // [B, H, Mpad], natural log-sum-exp of the scaled scores; -inf for a row without keys
+    float* delta;  // [B, H, Mpad]
+    MaskArgs mask;
+    int B, H, Hk, G;
+    float scale;
+};
+
 // Ordered compaction of per-tile flags (list[i] = flags of tile lo+i) into the visited list:
 // entry = (i) | flags << 10. One warp; returns the number of visited tiles.
 __device__ __forceinline__ int compact_visit_list(uint16_t* list, int n, int lane) {

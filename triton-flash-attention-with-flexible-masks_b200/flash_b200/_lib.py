@@ -8,7 +8,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
-FA_BF16, FA_FP16 = 0, 1
+FA_BF16, FA_FP16, FA_FP32 = 0, 1, 2
 FA_ID_NONE, FA_ID_INT32, FA_ID_INT64 = 0, 1, 2
 
 EXPORTS = (

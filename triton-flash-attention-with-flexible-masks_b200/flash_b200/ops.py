@@ -17,7 +17,9 @@ from . import _lib
 SCORE_FUNC_MODE0_NOPE = 0  # no extra mask
 SCORE_FUNC_MODE1_DOC = 1   # query id < 0: attend only to keys with the same id; id >= 0: attend to all
 
-_DTYPES = {torch.bfloat16: _lib.FA_BF16, torch.float16: _lib.FA_FP16}
+# bf16 / fp16 run on the tensor-core kernels; fp32 (accepted by the reference, flash_triton.py:512 and
+# testing.py:158) on fp32 FMA kernels that are exact to fp32 rounding but not fast
+_DTYPES = {torch.bfloat16: _lib.FA_BF16, torch.float16: _lib.FA_FP16, torch.float32: _lib.FA_FP32}
 _STATUS = {}  # device index -> int32[1] status word
 _SYNC_STATUS = os.environ.get("FA_B200_SYNC_STATUS", "0") not in ("", "0")
 # When set to a list, every kernel launch appends (name, start_event, end_event) recorded on the
@@ -138,7 +140,7 @@ def _problem(B, H, Hk, M, N, D, dtype, causal, mode, id_heads, sm_scale):
     p = _lib.Problem()
     p.B, p.H, p.Hk, p.M, p.N, p.D = B, H, Hk, M, N, D
     if dtype not in _DTYPES:
-        raise NotImplementedError(f"flash_b200 supports bf16 and fp16 inputs, got {dtype}")
+        raise NotImplementedError(f"flash_b200 supports bf16, fp16 and fp32 inputs, got {dtype}")
     p.dtype = _DTYPES[dtype]
     p.causal = 1 if causal else 0
     p.mode = int(mode)
@@ -195,8 +197,8 @@ class FlashAttention(torch.autograd.Function):
         _same_device(q, k=k, v=v, eq=eq, ek=ek)
         if k.dtype != q.dtype or v.dtype != q.dtype:
             raise ValueError(f"flash_b200: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
-        if D not in (64, 128):
-            raise NotImplementedError(f"flash_b200 implements head dims 64 and 128, got {D}")
+        if D not in (64, 128) and q.dtype != torch.float32:
+            raise NotImplementedError(f"flash_b200 implements head dims 64 and 128 for 16-bit inputs, got {D}")
         if sm_scale is None:
             sm_scale = 1. / math.sqrt(D)
         if not sm_scale > 0:
@@ -316,12 +318,12 @@ def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func
 def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
     """`attention` with the queries in the caller's order.
 
-    The kernels are built for head dims 64 and 128. The reference's smaller head dims (16 and 32,
-    flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
+    The tensor-core kernels are built for head dims 64 and 128. For 16-bit inputs the reference's smaller
+    head dims (16 and 32, flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
     nothing to q k^T, produce zero output columns, and their gradient columns are cut off again
     (autograd differentiates the padding and the slice)."""
     D = q.shape[-1]
-    if D in (16, 32) and k.shape[-1] == D and v.shape[-1] == D:
+    if D in (16, 32) and k.shape[-1] == D and v.shape[-1] == D and q.dtype != torch.float32:
         if sm_scale is None:
             sm_scale = 1. / math.sqrt(D)  # of the true head dim (flash_triton.py:523)
         pad = (0, 64 - D)
