@@ -146,6 +146,27 @@ int fa_fwd_static_plan(const fa_problem* p, const fa_tensor* q, const fa_tensor*
                        const fa_tensor* o, float* lse, const fa_ids* eq, const fa_ids* ek, int32_t* status,
                        void* stream);
 
+/* Largest query length fa_group_rows sorts (one CTA sorts a row in shared memory). */
+#define FA_GROUP_MAX_ROWS 16384
+
+/* Grouping of the queries by id for calls WITHOUT a causal mask, where the order of the query rows is
+ * free (no counterpart in the reference, which evaluates every tile whatever the ids,
+ * flash_triton.py:94-129). Sorts each id row of eq [B, id_heads, M] by the 32-bit code the mask plan
+ * uses for it (ids >= 0 share one code, which sorts last), stable, so rows that are grouped already keep
+ * their places. Writes three int32 arrays [B, id_heads, M], contiguous: `order` (grouped position ->
+ * caller's position), `inverse` (caller's position -> grouped position) and `grouped_ids` (the ids in
+ * grouped order; pass them as the eq of fa_plan_build). p->M <= FA_GROUP_MAX_ROWS, else
+ * FA_ERR_UNSUPPORTED. An id below -2^31 sets status 200 as in fa_plan_build. */
+int fa_group_rows(const fa_problem* p, const fa_ids* eq, int32_t* order, int32_t* inverse, int32_t* grouped_ids,
+                  int32_t* status, void* stream);
+
+/* dst[b, h, i, :] = src[b, h, index[b, he, i], :] for [B, H, M, D] tensors of p->dtype (he = h, or 0 when
+ * p->id_heads == 1); index is [B, id_heads, M] int32 with values in [0, M). With `order` it gathers q or dO
+ * into the grouped order, with `inverse` it puts o or dQ back. src and dst must not overlap; both need a
+ * 16-byte aligned base, last stride 1 and other strides that are whole 16-byte units. */
+int fa_permute_rows(const fa_problem* p, const fa_tensor* src, const fa_tensor* dst, const int32_t* index,
+                    void* stream);
+
 /* Test hook for the failure path (no counterpart in the reference, which has no failure handling):
  * one warp waits on a barrier nobody arrives at, with the kernels' own bounded wait and a limit of
  * `limit_clocks` SM clocks. The wait gives up, the kernel returns normally and `*status` holds

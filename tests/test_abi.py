@@ -134,3 +134,31 @@ def test_wait_test_hook_checks_its_arguments():
     assert lib.fa_debug_wait_timeout(None, 1000, 1, None) == 1
     assert lib.fa_debug_wait_timeout(st, 0, 1, None) == 1
     assert lib.fa_debug_wait_timeout(st, 1000, 98, None) == 1
+
+
+def test_group_and_permute_rows_check_their_arguments():
+    lib = _lib.load()
+    buf = (ctypes.c_int32 * 64)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p)
+    ids = _lib.Ids()
+    ids.ptr, ids.dtype = ptr.value, _lib.FA_ID_INT32
+    ids.stride[0], ids.stride[1], ids.stride[2] = 0, 0, 1
+    p = _prob(causal=0)
+    assert lib.fa_group_rows(ctypes.byref(p), None, ptr, ptr, ptr, ptr, None) == 1
+    assert lib.fa_group_rows(ctypes.byref(p), ctypes.byref(ids), None, ptr, ptr, ptr, None) == 1
+    assert lib.fa_group_rows(ctypes.byref(p), ctypes.byref(ids), ptr, ptr, ptr, None, None) == 1
+    assert lib.fa_group_rows(ctypes.byref(_prob(causal=0, mode=0)), ctypes.byref(ids), ptr, ptr, ptr, ptr, None) == 1
+    ids.dtype = 0
+    assert lib.fa_group_rows(ctypes.byref(p), ctypes.byref(ids), ptr, ptr, ptr, ptr, None) == 1
+    ids.dtype = _lib.FA_ID_INT32
+    too_long = _prob(causal=0, M=_lib.FA_GROUP_MAX_ROWS + 1, N=_lib.FA_GROUP_MAX_ROWS + 1)
+    assert lib.fa_group_rows(ctypes.byref(too_long), ctypes.byref(ids), ptr, ptr, ptr, ptr, None) == 2
+    t = _lib.Tensor()
+    assert lib.fa_permute_rows(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ptr, None) == 1  # null data
+    t.ptr = 4096 + 8  # not 16-byte aligned
+    t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 2 * 256 * 128, 256 * 128, 128, 1
+    assert lib.fa_permute_rows(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ptr, None) == 3
+    t.ptr = 4096
+    assert lib.fa_permute_rows(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), None, None) == 1
+    t.stride[2] = 132  # a row stride that is not a whole number of 16-byte units
+    assert lib.fa_permute_rows(ctypes.byref(p), ctypes.byref(t), ctypes.byref(t), ptr, None) == 3

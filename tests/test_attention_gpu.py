@@ -383,9 +383,11 @@ def test_small_head_dims_through_padding(fb, D):
 
 
 @pytest.mark.parametrize("per_head", [False, True])
-def test_query_gather_for_ungrouped_ids(fb, per_head):
-    """Random query ids, no causal mask (the layout of configuration 2): with GATHER_QUERIES the
-    queries are sorted by id for the kernels and the results come back in the caller's order."""
+def test_queries_grouped_by_id_without_causal_mask(fb, per_head):
+    """Random query ids, no causal mask (the layout of configuration 2): the default call sorts the
+    queries by id inside the library, runs the kernels on the grouped rows and returns the results in
+    the caller's order; with ops.GROUP_QUERIES off the same call runs in the caller's order. Both must
+    match the oracle, and the grouped call must visit fewer tiles."""
     from flash_b200 import ops
     g = torch.Generator().manual_seed(77)
     B, H, Hk, M, N, D = 2, 4, 2, 700, 1024, 64
@@ -398,16 +400,72 @@ def test_query_gather_for_ungrouped_ids(fb, per_head):
     eq[:, :, ::37] = 3  # some positions that attend to everything
     ek = -(torch.arange(N) // (N // 4) + 1)[None, None, :].expand(B, He, N).contiguous()
     eq, ek = eq.to("cuda").expand(B, H, M), ek.to("cuda").expand(B, H, N)
-    ops.GATHER_QUERIES = True
-    try:
-        o = fb.attention(q, k, v, False, None, eq, ek, 1)
-        o.backward(do)
-    finally:
-        ops.GATHER_QUERIES = False
+    assert ops.GROUP_QUERIES
     ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(),
                                                        False, None, eq.cpu(), ek.cpu(), 1)
-    close(o, ro, "O"); close(q.grad, rdq, "dQ"); close(k.grad, rdk, "dK"); close(v.grad, rdv, "dV")
+    for grouped in (True, False):
+        ops.GROUP_QUERIES = grouped
+        try:
+            q.grad = k.grad = v.grad = None
+            o = fb.attention(q, k, v, False, None, eq, ek, 1)
+            o.backward(do)
+        finally:
+            ops.GROUP_QUERIES = True
+        tag = "grouped" if grouped else "caller's order"
+        close(o, ro, f"O {tag}"); close(q.grad, rdq, f"dQ {tag}"); close(k.grad, rdk, f"dK {tag}")
+        close(v.grad, rdv, f"dV {tag}")
     fb.check_status()
+    # what grouping buys: visited tiles before and after
+    order, inverse, grouped_ids, id_heads = ops.group_rows(eq, B, H, M)
+    _, cls0 = fb.debug_mask(B, H, M, N, False, eq, ek, 1)
+    _, cls1 = fb.debug_mask(B, H, M, N, False, grouped_ids.expand(B, H, M), ek, 1)
+    v0, v1 = int((cls0 & 1).sum()), int((cls1 & 1).sum())
+    assert v1 < 0.6 * v0, (v0, v1)
+
+
+@pytest.mark.parametrize("M,He,dtype", [(1, 1, torch.int64), (129, 1, torch.int32), (700, 3, torch.int64),
+                                        (4096, 2, torch.int64), (16384, 1, torch.int64)])
+def test_group_rows_is_the_stable_sort_by_id_code(fb, M, He, dtype):
+    """fa_group_rows against torch's stable argsort of the id codes (ids >= 0 share the largest code):
+    order, inverse and the ids in the new order, for broadcast and per-head ids, int32 and int64."""
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(M + He)
+    B, H = 2, He if He > 1 else 4
+    ids = -(torch.randint(0, 9, (B, He, M), generator=g) + 1)
+    ids[torch.rand(B, He, M, generator=g) < 0.1] = 7
+    ids[torch.rand(B, He, M, generator=g) < 0.05] = 0
+    if dtype == torch.int64 and M > 1:
+        ids[0, 0, 1] = -(2 ** 31)  # the smallest id that still fits
+    ids = ids.to("cuda", dtype)
+    eq = ids.expand(B, H, M) if He == 1 else ids
+    order, inverse, grouped, id_heads = ops.group_rows(eq, B, H, M)
+    fb.check_status()
+    assert id_heads == He and order.shape == (B, He, M)
+    code = torch.where(ids >= 0, torch.full_like(ids, 2 ** 31 - 1), ids).to(torch.int64)
+    want = torch.argsort(code, dim=-1, stable=True)
+    assert torch.equal(order.long(), want)
+    assert torch.equal(torch.gather(inverse.long(), -1, want), torch.arange(M, device="cuda").expand(B, He, M))
+    assert torch.equal(grouped.long(), torch.gather(code, -1, want))
+    # grouped ids keep the mask: ids >= 0 come back as a non-negative id
+    assert bool(((grouped >= 0) == (torch.gather(ids, -1, want) >= 0)).all())
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64), (torch.float32, 16)])
+def test_permute_rows_moves_rows_exactly(fb, dtype, D):
+    from flash_b200 import ops
+    g = torch.Generator().manual_seed(D)
+    B, H, M = 2, 3, 333
+    x = torch.randn(B, H, M, D, generator=g).to("cuda", dtype)
+    for He in (1, H):
+        index = torch.stack([torch.stack([torch.randperm(M, generator=g) for _ in range(He)]) for _ in range(B)])
+        index = index.to("cuda", torch.int32)
+        y = ops._permute_rows(x, index, He)
+        want = torch.gather(x, 2, index.long().expand(B, H, M)[..., None].expand(B, H, M, D))
+        assert torch.equal(y, want)
+        # a strided source (a slice of a wider tensor)
+        wide = torch.randn(B, H, M, 2 * D, generator=g).to("cuda", dtype)
+        y2 = ops._permute_rows(wide[..., :D], index, He)
+        assert torch.equal(y2, torch.gather(wide[..., :D], 2, index.long().expand(B, H, M)[..., None].expand(B, H, M, D)))
 
 
 def test_unsupported_inputs_raise(fb):

@@ -10,11 +10,12 @@ LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
 FA_BF16, FA_FP16, FA_FP32 = 0, 1, 2
 FA_ID_NONE, FA_ID_INT32, FA_ID_INT64 = 0, 1, 2
+FA_GROUP_MAX_ROWS = 16384
 
 EXPORTS = (
     "fa_version", "fa_error_string", "fa_padded_rows", "fa_plan_bytes", "fa_plan_build", "fa_fwd",
     "fa_bwd_delta", "fa_bwd_dkdv", "fa_bwd_dq", "fa_debug_mask", "fa_classify_tile", "fa_fwd_static_plan",
-    "fa_debug_wait_timeout",
+    "fa_debug_wait_timeout", "fa_group_rows", "fa_permute_rows",
 )
 
 
@@ -73,6 +74,10 @@ def load():
     lib.fa_fwd_static_plan.argtypes = [P, T, T, T, T, vp, I, I, vp, vp]
     lib.fa_debug_wait_timeout.restype = i32
     lib.fa_debug_wait_timeout.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, vp]
+    lib.fa_group_rows.restype = i32
+    lib.fa_group_rows.argtypes = [P, I, vp, vp, vp, vp, vp]
+    lib.fa_permute_rows.restype = i32
+    lib.fa_permute_rows.argtypes = [P, T, T, vp, vp]
     lib.fa_classify_tile.restype = ctypes.c_uint32
     lib.fa_classify_tile.argtypes = [ctypes.c_int32] * 10
     _lib = lib

@@ -108,8 +108,9 @@ def attention_host(q, k, v, do=None, causal=False, sm_scale=None, eq=None, ek=No
         if name not in out:
             out[name] = torch.empty(like.shape, dtype=like.dtype).pin_memory()
     dim, slices = _slices(B, H, Hk, parts)
-    # other head dims go through the padding of `ops.attention`, and so does the optional query gather
-    gather = ops.GATHER_QUERIES and score_func_mode == ops.SCORE_FUNC_MODE1_DOC and not causal
+    # other head dims go through the padding of `ops.attention`, and so does the grouping of the queries of
+    # calls without a causal mask
+    gather = ops.GROUP_QUERIES and score_func_mode == ops.SCORE_FUNC_MODE1_DOC and not causal
     direct = D in (64, 128) and not gather
     with torch.cuda.device(dev):
         cur = torch.cuda.current_stream()

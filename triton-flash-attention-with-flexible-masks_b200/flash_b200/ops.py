@@ -288,35 +288,74 @@ class FlashAttention(torch.autograd.Function):
 
 
 # Without a causal mask the order of the queries is free. When the query ids are not grouped (every
-# block of 128 queries holds every document) no tile can be skipped and every tile needs the id check;
-# with GATHER_QUERIES = True the queries of such calls are first sorted by id (a stable sort: grouped
-# ids stay as they are), which makes the blocks (nearly) uniform again, and the results are put back
-# in the caller's order. Off by default: it costs a gather of q and a scatter of o / dq per call.
-GATHER_QUERIES = False
+# block of 128 queries holds every document) no tile can be skipped and every tile needs the id check.
+# Calls in document mode without a causal mask therefore first sort the query rows by id inside the
+# library (fa_group_rows: a stable sort, so ids that are grouped already keep their places), run the
+# kernels on the grouped rows, whose blocks are (nearly) uniform again, and put o back in the caller's
+# order; backward does the same with dO and dQ. The cost is one sort of the ids and two row permutations
+# per pass. GROUP_QUERIES = False (or FA_B200_GROUP_QUERIES=0 in the environment) runs such calls in the
+# caller's order. Longer rows than the library sorts (FA_GROUP_MAX_ROWS) always run in the caller's order.
+GROUP_QUERIES = os.environ.get("FA_B200_GROUP_QUERIES", "1") not in ("", "0")
 
 
-def _attention_gathered(q, k, v, sm_scale, eq, ek):
-    B, H, M, D = q.shape
+def _permute_rows(x, index, id_heads):
+    """out[b, h, i, :] = x[b, h, index[b, he, i], :] by the library's row-permutation kernel."""
+    lib = _lib.load()
+    x = maybe_contiguous(x)
+    B, H, M, D = x.shape
+    out = torch.empty((B, H, M, D), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        prob = _problem(B, H, H, M, M, D, x.dtype, False, SCORE_FUNC_MODE1_DOC, id_heads, 1.0)
+        tx, to = _tensor(x), _tensor(out)
+        with _Timed("permute"):
+            _lib.check(lib.fa_permute_rows(ctypes.byref(prob), ctypes.byref(tx), ctypes.byref(to), index.data_ptr(),
+                                           _stream()), "fa_permute_rows")
+    return out
+
+
+class _PermuteRows(torch.autograd.Function):
+    """y[..., i, :] = x[..., index[i], :]; the gradient moves through the inverse permutation."""
+
+    @staticmethod
+    def forward(ctx, x, index, inverse, id_heads):
+        ctx.save_for_backward(inverse)
+        ctx.id_heads = id_heads
+        return _permute_rows(x, index, id_heads)
+
+    @staticmethod
+    def backward(ctx, g):
+        inverse, = ctx.saved_tensors
+        return _permute_rows(g, inverse, ctx.id_heads), None, None, None
+
+
+def group_rows(eq, B, H, M):
+    """(order, inverse, grouped_ids, id_heads): the stable sort of each id row of eq [B, H, M] by the mask's
+    id code, as int32 tensors [B, id_heads, M] (id_heads is 1 when eq is broadcast over the heads)."""
+    lib = _lib.load()
     eq = _id_tensor(eq, B, H, M, "eq")
-    shared = (H == 1) or eq.stride(1) == 0  # one id row per batch, broadcast over the heads
-    rows = eq[:, :1] if shared else eq
-    perm = torch.argsort(rows, dim=-1, stable=True)                      # [B, 1|H, M]
-    inv = torch.empty_like(perm).scatter_(-1, perm, torch.arange(M, device=q.device).expand_as(perm))
-    eq_s = torch.gather(rows, -1, perm).expand(B, H, M)
-    idx = perm.expand(B, H, M)[..., None].expand(B, H, M, D)
-    o_s = attention_ungathered(torch.gather(q, 2, idx), k, v, False, sm_scale, eq_s, ek, SCORE_FUNC_MODE1_DOC)
-    return torch.gather(o_s, 2, inv.expand(B, H, M)[..., None].expand(B, H, M, D))
+    id_heads = 1 if (H == 1 or eq.stride(1) == 0) else H
+    with torch.cuda.device(eq.device):
+        out = torch.empty((3, B, id_heads, M), dtype=torch.int32, device=eq.device)
+        prob = _problem(B, H, H, M, M, 64, torch.bfloat16, False, SCORE_FUNC_MODE1_DOC, id_heads, 1.0)
+        ieq = _ids(eq)
+        status = _status_word(eq.device)
+        with _Timed("group"):
+            _lib.check(lib.fa_group_rows(ctypes.byref(prob), ctypes.byref(ieq), out[0].data_ptr(), out[1].data_ptr(),
+                                         out[2].data_ptr(), status.data_ptr(), _stream()), "fa_group_rows")
+    return out[0], out[1], out[2], id_heads
+
+
+def _attention_grouped(q, k, v, sm_scale, eq, ek):
+    B, H, M, D = q.shape
+    _same_device(q, eq=eq)
+    order, inverse, grouped, id_heads = group_rows(eq, B, H, M)
+    q_g = _PermuteRows.apply(q, order, inverse, id_heads)
+    o_g = FlashAttention.apply(q_g, k, v, False, sm_scale, grouped.expand(B, H, M), ek, SCORE_FUNC_MODE1_DOC)
+    return _PermuteRows.apply(o_g, inverse, order, id_heads)
 
 
 def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
-    """Drop-in for flash_triton.py:640-641."""
-    if GATHER_QUERIES and score_func_mode == SCORE_FUNC_MODE1_DOC and not causal and eq is not None and q.is_cuda:
-        return _attention_gathered(q, k, v, sm_scale, eq, ek)
-    return attention_ungathered(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
-
-
-def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
-    """`attention` with the queries in the caller's order.
+    """Drop-in for flash_triton.py:640-641.
 
     The tensor-core kernels are built for head dims 64 and 128. For 16-bit inputs the reference's smaller
     head dims (16 and 32, flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
@@ -328,8 +367,25 @@ def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None,
             sm_scale = 1. / math.sqrt(D)  # of the true head dim (flash_triton.py:523)
         pad = (0, 64 - D)
         q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
-        return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)[..., :D]
+        return _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)[..., :D]
+    return _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
+
+
+def _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode):
+    if (GROUP_QUERIES and score_func_mode == SCORE_FUNC_MODE1_DOC and not causal and eq is not None and ek is not None
+            and q.is_cuda and q.dim() == 4 and 128 < q.shape[2] <= _lib.FA_GROUP_MAX_ROWS):
+        return _attention_grouped(q, k, v, sm_scale, eq, ek)
     return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
+
+
+def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
+    """`attention` with the queries in the caller's order, whatever GROUP_QUERIES says."""
+    global GROUP_QUERIES
+    saved, GROUP_QUERIES = GROUP_QUERIES, False
+    try:
+        return attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
+    finally:
+        GROUP_QUERIES = saved
 
 
 def debug_mask(B, H, M, N, causal, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE, device="cuda"):
