@@ -38,8 +38,11 @@ extern "C" {
 
 #define FA_VERSION 1
 
-/* FA_FP32 tensors (4-byte aligned base, last stride 1, any positive other strides) take fp32 FMA kernels that
- * cover head dims 16, 32, 64 and 128 (flash_triton.py:512; testing.py:158): exact to fp32 rounding, not fast. */
+/* Head dims 16, 32, 64 and 128 (flash_triton.py:512). FA_BF16 / FA_FP16 run on tensor-core kernels built for 64
+ * and 128 columns; with head dims 16 and 32 the 64-wide kernels read the tensors through TMA maps of the real
+ * head dim, which fill the missing columns with zeros and never write them (no padded copies anywhere).
+ * FA_FP32 tensors (4-byte aligned base, last stride 1, any positive other strides) take fp32 FMA kernels
+ * (testing.py:158): exact to fp32 rounding, not fast. */
 enum fa_dtype { FA_BF16 = 0, FA_FP16 = 1, FA_FP32 = 2 };
 enum fa_id_dtype { FA_ID_NONE = 0, FA_ID_INT32 = 1, FA_ID_INT64 = 2 };
 /* score_func_mode of the reference (flash_triton.py:20-22) */
@@ -48,7 +51,7 @@ enum fa_mode { FA_MODE0_NOPE = 0, FA_MODE1_DOC = 1 };
 enum fa_error {
     FA_OK = 0,
     FA_ERR_BAD_ARG = 1,      /* null pointer, non-positive size, unknown enum */
-    FA_ERR_UNSUPPORTED = 2,  /* head dim not in {64,128} (fp32: {16,32,64,128}), unknown dtype, sm_scale <= 0 */
+    FA_ERR_UNSUPPORTED = 2,  /* head dim not in {16,32,64,128}, unknown dtype, sm_scale <= 0 */
     FA_ERR_ALIGNMENT = 3,    /* a base address or stride breaks the TMA 16-byte rules */
     FA_ERR_TENSORMAP = 4,    /* the driver refused to encode a tensor map */
     FA_ERR_LAUNCH = 5,       /* kernel launch failed (cudaGetLastError) */

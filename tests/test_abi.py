@@ -57,7 +57,7 @@ def test_plan_bytes():
 
 
 @pytest.mark.parametrize("kw,code", [
-    (dict(D=32), 2), (dict(D=256), 2), (dict(D=48, dtype=2), 2), (dict(dtype=5), 2), (dict(sm_scale=0.0), 2), (dict(sm_scale=-1.0), 2),
+    (dict(D=48), 2), (dict(D=256), 2), (dict(D=8), 2), (dict(D=48, dtype=2), 2), (dict(dtype=5), 2), (dict(sm_scale=0.0), 2), (dict(sm_scale=-1.0), 2),
     (dict(H=3, Hk=2), 1), (dict(M=0), 1), (dict(mode=7), 1), (dict(M=512, N=256, causal=1), 1),
     (dict(id_heads=3), 1), (dict(N=128 * 1024 + 1, M=128), 2),
 ])
@@ -67,11 +67,12 @@ def test_bad_problems_are_refused(kw, code):
     assert lib.fa_plan_bytes(ctypes.byref(_prob(**kw)), ctypes.byref(n)) == code
 
 
-def test_fp32_problems_take_every_head_dim_of_the_reference():
+def test_every_dtype_takes_every_head_dim_of_the_reference():
     lib = _lib.load()
     n = ctypes.c_size_t(0)
-    for D in (16, 32, 64, 128):
-        assert lib.fa_plan_bytes(ctypes.byref(_prob(D=D, dtype=2)), ctypes.byref(n)) == 0
+    for dtype in (0, 1, 2):
+        for D in (16, 32, 64, 128):
+            assert lib.fa_plan_bytes(ctypes.byref(_prob(D=D, dtype=dtype)), ctypes.byref(n)) == 0
 
 
 def test_forward_refuses_bad_tensors_without_a_gpu():

@@ -361,24 +361,35 @@ def test_strided_inputs_and_custom_scale(fb):
     fb.check_status()
 
 
-@pytest.mark.parametrize("D", [16, 32])
-def test_small_head_dims_through_padding(fb, D):
-    """Head dims 16 and 32 of the reference (flash_triton.py:512) run on zero-padded copies."""
+@pytest.mark.parametrize("D,dtype,causal", [(16, BF, True), (32, BF, True), (32, torch.float16, False), (16, torch.float16, False)])
+def test_small_head_dims_without_padded_copies(fb, D, dtype, causal):
+    """Head dims 16 and 32 of the reference (flash_triton.py:512) run on the 64-wide kernels through tensor maps of
+    the real head dim: no padded copy is made (the inputs are slices of wider tensors whose neighbouring columns
+    hold NaN: nothing outside the D real columns may be read into the result, and nothing outside may be written)."""
     g = torch.Generator().manual_seed(40 + D)
     B, H, Hk, M, N = 2, 4, 2, 300, 430
-    q = torch.randn(B, H, M, D, generator=g).to("cuda", BF).requires_grad_()
-    k = torch.randn(B, Hk, N, D, generator=g).to("cuda", BF).requires_grad_()
-    v = torch.randn(B, Hk, N, D, generator=g).to("cuda", BF).requires_grad_()
-    do = torch.randn(B, H, M, D, generator=g).to("cuda", BF)
+    def wide(h, L):
+        t = torch.full((B, h, L, 64), float("nan"), dtype=dtype, device="cuda")
+        t[..., :D] = torch.randn(B, h, L, D, generator=g).to("cuda", dtype)
+        return t
+    wq, wk, wv = wide(H, M), wide(Hk, N), wide(Hk, N)
+    q, k, v = [t[..., :D].detach().requires_grad_() for t in (wq, wk, wv)]  # strided views, row stride 64
+    do = torch.randn(B, H, M, D, generator=g).to("cuda", dtype)
     rng = np.random.default_rng(D)
     eq = make_ids(B, H, N, 3, 0.05, rng).to("cuda")
-    o = fb.attention(q, k, v, True, None, eq[:, :, :M], eq, 1)
+    before = torch.cuda.memory_allocated()
+    o = fb.attention(q, k, v, causal, None, eq[:, :, :M], eq, 1)
     assert o.shape == (B, H, M, D)
+    # forward allocates O, LSE, the plan and (without a causal mask) the grouped q / o and the sort's index arrays: no
+    # 64-wide copies of q, k, v
+    small = 4 * B * H * M * D * 2 + B * H * 384 * 4 + (1 << 16)
+    assert torch.cuda.memory_allocated() - before < small + 2 * B * Hk * N * D * 2
     o.backward(do)
     ro, rdq, rdk, rdv = orc.attention_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(),
-                                                       True, None, eq[:, :, :M].cpu(), eq.cpu(), 1)
+                                                       causal, None, eq[:, :, :M].cpu(), eq.cpu(), 1)
     close(o, ro, "O"); close(q.grad, rdq, "dQ"); close(k.grad, rdk, "dK"); close(v.grad, rdv, "dV")
     assert q.grad.shape == q.shape and k.grad.shape == k.shape
+    assert torch.isnan(wq[..., D:]).all() and torch.isnan(wk[..., D:]).all()  # the neighbouring columns are untouched
     fb.check_status()
 
 

@@ -54,7 +54,10 @@ int check_problem(const fa_problem* p) {
     if (p->dtype == FA_FP32) {  // fp32 FMA kernels: every head dim of the reference (flash_triton.py:512)
         if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
     } else {
-        if (p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
+        // Head dims 16 and 32 run on the 64-wide tensor-core kernels: their tensor maps cover the real head
+        // dim, so the TMA loads fill the missing columns of each 64-column box with zeros (they add nothing
+        // to Q K^T and give zero output columns) and the TMA stores write the real columns only.
+        if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) return FA_ERR_UNSUPPORTED;
         if (p->dtype != FA_BF16 && p->dtype != FA_FP16) return FA_ERR_UNSUPPORTED;
     }
     if (!(p->sm_scale > 0.f)) return FA_ERR_UNSUPPORTED;
@@ -92,7 +95,7 @@ fa::F32Tensor f32_view(const fa_tensor* t) {
 }
 
 // 4-D map over [B, H, L, D]; box = 64 elements of D x 128 rows of L; 128-byte swizzle; rows
-// outside [0, L) read as zero.
+// outside [0, L) and (head dims 16 and 32) columns outside [0, D) read as zero and are not written.
 int make_map(CUtensorMap* out, const fa_tensor* t, int dtype, int B, int H, int L, int D) {
     EncodeFn fn = encode_fn();
     if (!fn) return FA_ERR_NO_DRIVER;
@@ -230,8 +233,8 @@ const char* fa_error_string(int code) {
         case FA_OK: return "ok";
         case FA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, H % Hk != 0, causal with N < M)";
         case FA_ERR_UNSUPPORTED:
-            return "unsupported problem (head dim must be 64 or 128 for bf16/fp16 and 16, 32, 64 or 128 for fp32, "
-                   "sm_scale > 0, at most 131072 tokens per sequence)";
+            return "unsupported problem (head dim must be 16, 32, 64 or 128, dtype bf16, fp16 or fp32, sm_scale > 0, "
+                   "at most 131072 tokens per sequence)";
         case FA_ERR_ALIGNMENT:
             return "a buffer breaks the alignment rules (tensors: 16-byte aligned base, last stride 1, other strides "
                    "multiples of 8; lse, delta and plan: 16-byte aligned)";

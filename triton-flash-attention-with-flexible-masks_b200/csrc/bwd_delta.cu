@@ -8,15 +8,16 @@
 
 namespace fa {
 
-// 8 threads per row, 16 rows per CTA of 128 threads; each thread reads D/8 contiguous elements.
+// 8 threads per row, 16 rows per CTA of 128 threads; each thread reads D/8 contiguous elements (at least 8:
+// with head dims 16 and 32 only the first 2 or 4 threads of a row have any).
 template <int D, bool BF16>
 __global__ void __launch_bounds__(128) bwd_delta_kernel(const DeltaParams p) {
     const int h = blockIdx.y, b = blockIdx.z;
     const int row = blockIdx.x * 16 + (threadIdx.x >> 3);
     const int part = threadIdx.x & 7;
-    constexpr int PER = D / 8;  // elements per thread: 16 (D=128) or 8 (D=64)
+    constexpr int PER = (D >= 64) ? D / 8 : 8;  // elements per thread: 16 (D=128) or 8
     float acc = 0.f;
-    if (row < p.M) {
+    if (row < p.M && part * PER < D) {
         const uint8_t* po = static_cast<const uint8_t*>(p.o.ptr) +
                             2 * (int64_t(b) * p.o.sb + int64_t(h) * p.o.sh + int64_t(row) * p.o.sl + part * PER);
         const uint8_t* pd = static_cast<const uint8_t*>(p.d_o.ptr) +
@@ -55,6 +56,12 @@ cudaError_t launch_bwd_delta(const DeltaParams& p, cudaStream_t stream) {
     if (p.D == 128) {
         if (p.bf16) bwd_delta_kernel<128, true><<<grid, 128, 0, stream>>>(p);
         else bwd_delta_kernel<128, false><<<grid, 128, 0, stream>>>(p);
+    } else if (p.D == 32) {
+        if (p.bf16) bwd_delta_kernel<32, true><<<grid, 128, 0, stream>>>(p);
+        else bwd_delta_kernel<32, false><<<grid, 128, 0, stream>>>(p);
+    } else if (p.D == 16) {
+        if (p.bf16) bwd_delta_kernel<16, true><<<grid, 128, 0, stream>>>(p);
+        else bwd_delta_kernel<16, false><<<grid, 128, 0, stream>>>(p);
     } else {
         if (p.bf16) bwd_delta_kernel<64, true><<<grid, 128, 0, stream>>>(p);
         else bwd_delta_kernel<64, false><<<grid, 128, 0, stream>>>(p);

@@ -108,10 +108,9 @@ def attention_host(q, k, v, do=None, causal=False, sm_scale=None, eq=None, ek=No
         if name not in out:
             out[name] = torch.empty(like.shape, dtype=like.dtype).pin_memory()
     dim, slices = _slices(B, H, Hk, parts)
-    # other head dims go through the padding of `ops.attention`, and so does the grouping of the queries of
-    # calls without a causal mask
+    # calls without a causal mask go through `ops.attention`, which groups their queries by id first
     gather = ops.GROUP_QUERIES and score_func_mode == ops.SCORE_FUNC_MODE1_DOC and not causal
-    direct = D in (64, 128) and not gather
+    direct = not gather
     with torch.cuda.device(dev):
         cur = torch.cuda.current_stream()
         s_in, s_cmp, s_out = _side_streams(dev)

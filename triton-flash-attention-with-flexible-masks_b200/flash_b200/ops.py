@@ -197,8 +197,6 @@ class FlashAttention(torch.autograd.Function):
         _same_device(q, k=k, v=v, eq=eq, ek=ek)
         if k.dtype != q.dtype or v.dtype != q.dtype:
             raise ValueError(f"flash_b200: q, k, v must share one dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
-        if D not in (64, 128) and q.dtype != torch.float32:
-            raise NotImplementedError(f"flash_b200 implements head dims 64 and 128 for 16-bit inputs, got {D}")
         if sm_scale is None:
             sm_scale = 1. / math.sqrt(D)
         if not sm_scale > 0:
@@ -358,16 +356,10 @@ def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func
     """Drop-in for flash_triton.py:640-641.
 
     The tensor-core kernels are built for head dims 64 and 128. For 16-bit inputs the reference's smaller
-    head dims (16 and 32, flash_triton.py:512) run through the 64-wide kernels on zero-padded copies: zero columns add
-    nothing to q k^T, produce zero output columns, and their gradient columns are cut off again
-    (autograd differentiates the padding and the slice)."""
-    D = q.shape[-1]
-    if D in (16, 32) and k.shape[-1] == D and v.shape[-1] == D and q.dtype != torch.float32:
-        if sm_scale is None:
-            sm_scale = 1. / math.sqrt(D)  # of the true head dim (flash_triton.py:523)
-        pad = (0, 64 - D)
-        q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
-        return _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)[..., :D]
+    head dims (16 and 32, flash_triton.py:512) run on the 64-wide kernels without any padded copy: the library
+    describes the tensors to the TMA unit with their real head dim, the loads fill the missing columns of a
+    tile with zeros (zero columns add nothing to q k^T and give zero output columns) and the stores write the
+    real columns only."""
     return _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
 
 
