@@ -83,24 +83,30 @@ def test_fixed_order_without_plan_matches_counters(monkeypatch, causal):
         assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("B,H,Hk,mode", [(1, 8, 4, 1), (3, 4, 4, 1), (1, 4, 4, 0)])
-def test_attention_host_matches_attention(B, H, Hk, mode):
-    """The streamed call for host tensors computes slices of heads (or batches) on their own: same bits."""
+@pytest.mark.parametrize("B,H,Hk,mode,causal,D", [(1, 8, 4, 1, True, 64), (3, 4, 4, 1, True, 64), (1, 4, 4, 0, True, 64),
+                                                  (2, 4, 2, 1, False, 32)])
+def test_attention_host_matches_attention(B, H, Hk, mode, causal, D):
+    """The streamed call for host tensors computes slices of heads (or batches) on their own: same bits. The last
+    case has no causal mask (its queries are grouped by id inside the library) and a head dim below 64."""
     import flash_b200 as fb
     dev = torch.device("cuda", 0)
-    L, D = 640, 64
+    L = 640
     g = torch.Generator().manual_seed(13)
     q = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16).pin_memory()
     k, v = [torch.randn(B, Hk, L, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(2)]
     do = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16).pin_memory()
     ids = torch.from_numpy(_doc_ids(L, [100, 333]))[None, None, :].repeat(B, 1, 1) if mode == 1 else None
+    idq = ids
+    if mode == 1 and not causal:  # scattered query ids
+        idq = ids[..., torch.randperm(L, generator=g)].contiguous()
     # the device defaults to the current one
-    res = fb.attention_host(q, k, v, do, True, 0.125, ids, ids, mode, parts=3, **({} if mode == 0 else {"device": dev}))
+    res = fb.attention_host(q, k, v, do, causal, 0.125, idq, ids, mode, parts=3, **({} if mode == 0 else {"device": dev}))
     torch.cuda.synchronize()
     fb.check_status()
     qd, kd, vd = [t.to(dev).requires_grad_() for t in (q, k, v)]
     idd = ids.to(dev).expand(B, H, L) if ids is not None else None
-    o = fb.attention(qd, kd, vd, True, 0.125, idd, idd, mode)
+    idqd = idq.to(dev).expand(B, H, L) if ids is not None else None
+    o = fb.attention(qd, kd, vd, causal, 0.125, idqd, idd, mode)
     o.backward(do.to(dev))
     torch.cuda.synchronize()
     for name, ref in (("o", o.detach()), ("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
