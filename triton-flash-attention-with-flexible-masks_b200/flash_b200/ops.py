@@ -360,24 +360,10 @@ def attention(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func
     describes the tensors to the TMA unit with their real head dim, the loads fill the missing columns of a
     tile with zeros (zero columns add nothing to q k^T and give zero output columns) and the stores write the
     real columns only."""
-    return _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
-
-
-def _attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode):
     if (GROUP_QUERIES and score_func_mode == SCORE_FUNC_MODE1_DOC and not causal and eq is not None and ek is not None
             and q.is_cuda and q.dim() == 4 and 128 < q.shape[2] <= _lib.FA_GROUP_MAX_ROWS):
         return _attention_grouped(q, k, v, sm_scale, eq, ek)
     return FlashAttention.apply(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
-
-
-def attention_ungathered(q, k, v, causal=False, sm_scale=None, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE):
-    """`attention` with the queries in the caller's order, whatever GROUP_QUERIES says."""
-    global GROUP_QUERIES
-    saved, GROUP_QUERIES = GROUP_QUERIES, False
-    try:
-        return attention(q, k, v, causal, sm_scale, eq, ek, score_func_mode)
-    finally:
-        GROUP_QUERIES = saved
 
 
 def debug_mask(B, H, M, N, causal, eq=None, ek=None, score_func_mode=SCORE_FUNC_MODE0_NOPE, device="cuda"):
