@@ -131,12 +131,16 @@ extern "C" int fa_group_rows(const fa_problem* p, const fa_ids* eq, int32_t* ord
     int P = 1;
     while (P < p->M) P <<= 1;
     const size_t smem = size_t(P) * sizeof(unsigned long long);
-    static bool attr_set = false;  // the same value every time: a race between two first calls is harmless
-    if (!attr_set) {
+    // the attribute belongs to the device: set it once per device (always the same value, so a race between two
+    // first calls is harmless)
+    static bool attr_set[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FA_ERR_LAUNCH;
+    if (!attr_set[dev]) {
         if (cudaFuncSetAttribute(group_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(FA_GROUP_MAX_ROWS * sizeof(unsigned long long))) != cudaSuccess)
             return FA_ERR_LAUNCH;
-        attr_set = true;
+        attr_set[dev] = true;
     }
     const IdRows rows{eq->ptr, eq->stride[0], eq->stride[1], eq->stride[2], eq->dtype == FA_ID_INT64};
     group_rows_kernel<<<dim3(p->id_heads, p->B), kSortThreads, smem, static_cast<cudaStream_t>(stream)>>>(
